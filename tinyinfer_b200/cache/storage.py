@@ -1,5 +1,6 @@
 """Device memory behind the page ids: for every cache entry that wants pages one tensor
-[2, pages, kv_heads, page_size, head_dim] (keys then values; one (page, head) tile of
+[planes, pages, kv_heads, page_size, head_dim] (two planes: keys then values; one plane: a row per token
+from which both are made; one (page, head) tile of
 page_size x head_dim is contiguous, which is what a tiled copy wants), and for every entry that
 wants per-request state one tensor [slots, *shape].
 
@@ -20,7 +21,7 @@ def bytes_per_page(needs, page_size: int, dtype: torch.dtype) -> int:
     total = 0
     for need, _state in needs:
         if need is not None:
-            total += 2 * need.num_kv_heads * page_size * need.head_dim * dtype.itemsize
+            total += need.planes * need.num_kv_heads * page_size * need.head_dim * dtype.itemsize
     return total
 
 
@@ -37,7 +38,7 @@ class CacheStorage:
                 # one page more than the pool hands out: the last one takes the keys of the padding rows
                 # that fill a decode batch up to the size of its captured graph (see dump_page)
                 pages = manager.groups[manager.group_of_entry[entry]].pool.num_pages + 1
-                shape = (2, pages, need.num_kv_heads, manager.page_size, need.head_dim)
+                shape = (need.planes, pages, need.num_kv_heads, manager.page_size, need.head_dim)
                 t = torch.empty(shape, dtype=dtype, device=self.device)
                 # tests poison the pool: a read outside a request's own keys then shows as NaN
                 t.fill_(float("nan") if poison else 0.0)

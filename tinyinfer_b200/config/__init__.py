@@ -4,10 +4,11 @@ from .registry import (Architecture, architecture_of, known_architectures, known
 from .specs import (AttentionSpec, ExecStep, GatedMLPSpec, LayerSpec, ModelSpec, NormSpec,
                     PositionSpec, TensorNames, default_execution)
 from .qwen3 import Qwen3Config
+from .gulisun import GulisunConfig
 
 __all__ = [
     "EngineConfig", "parse_dtype", "Architecture", "architecture_of", "known_architectures",
     "known_presets", "load_config", "lookup_architecture", "preset_config", "register_architecture", "AttentionSpec", "ExecStep",
     "GatedMLPSpec", "LayerSpec", "ModelSpec", "NormSpec", "PositionSpec", "TensorNames",
-    "default_execution", "Qwen3Config",
+    "default_execution", "Qwen3Config", "GulisunConfig",
 ]

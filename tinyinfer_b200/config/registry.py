@@ -62,8 +62,10 @@ def lookup_architecture(name: str) -> Architecture:
 
 def architecture_of(config_dict: dict) -> Architecture:
     names = config_dict.get("architectures")
+    if names is None and isinstance(config_dict.get("architecture"), str):
+        names = [config_dict["architecture"]]          # some designs name themselves with one string
     if not isinstance(names, (list, tuple)) or not names:
-        raise ValueError("config.json has no 'architectures' list; known: "
+        raise ValueError("config.json has neither an 'architectures' list nor an 'architecture' name; known: "
                          f"{known_architectures()}")
     return lookup_architecture(names[0])
 

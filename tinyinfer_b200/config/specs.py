@@ -18,6 +18,7 @@ class NormSpec:
     size: int
     eps: float
     kind: str = "rmsnorm"
+    tensor: str = "weight"                  # local name of the weight behind the norm's prefix ('' : the prefix itself)
 
 
 @dataclass(frozen=True)
@@ -28,6 +29,7 @@ class PositionSpec:
     kind: str = "rope"
     theta: float = 10000.0
     rotary_dim: int = 0
+    exact_frequencies: bool = False         # inv_freq worked out in float64 and rounded once (default: in float32)
 
 
 @dataclass(frozen=True)
@@ -63,13 +65,66 @@ class GatedMLPSpec:
 
 
 @dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Softmax attention whose keys and values are linear maps of one cached low-rank latent per token, with the
+    queries through a latent of their own. Per head ``head_dim`` unrotated and ``rot_dim`` rotated query/key
+    features (the rotated key part is one vector shared by all heads) and ``v_dim`` value features.
+    ``sink``: a learned number per head whose exponential joins the softmax denominator.
+    ``shares_cache``: the layer has no key/value down projection and reads the rows another layer caches."""
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    rot_dim: int
+    v_dim: int
+    q_rank: int
+    kv_rank: int
+    scale: float
+    position: PositionSpec
+    norm_eps: float
+    sink: bool = False
+    shares_cache: bool = False
+    window: Optional[int] = None
+    kind: str = "latent_attention"
+
+
+@dataclass(frozen=True)
+class GatedRecurrenceSpec:
+    """Recurrent block: out = W_o (S * gelu_tanh(W_y h + b)), S the state of a real-gated diagonal linear
+    recurrence a = exp(-decay * r * softplus(lam)) driven by a causal per-channel convolution of W_x h + b;
+    the gates r and i are block-diagonal maps (``blocks`` square blocks) of the convolution's output."""
+    hidden_size: int
+    width: int
+    blocks: int
+    conv_taps: int
+    decay: float = 8.0
+    kind: str = "gated_recurrence"
+
+
+@dataclass(frozen=True)
+class ExpertsSpec:
+    """Mixture of experts: every token runs the ``top`` experts with the largest softmax scores, weighted by
+    those scores over their sum (+ ``weight_eps``); an expert is down(act(up h)) without biases.
+    ``shared_size`` > 0: one more expert of that inner size runs for every token and is added."""
+    hidden_size: int
+    num_experts: int
+    top: int
+    expert_size: int
+    shared_size: int = 0
+    activation: str = "relu_squared"
+    weight_eps: float = 1e-20
+    kind: str = "experts"
+
+
+@dataclass(frozen=True)
 class LayerSpec:
     """One block: which mixer, which feed-forward, their norms and how they are arranged.
-    ``arrangement='pre_norm'``: x += mixer(norm1(x)); x += feed_forward(norm2(x))."""
+    ``arrangement='pre_norm'``: x += mixer(norm1(x)); x += feed_forward(norm2(x)).
+    ``arrangement='output_norm'``: x += norm1(mixer(x)); x += norm2(feed_forward(x)), the sums in a float32 stream.
+    ``feed_forward`` None (with ``feed_forward_norm`` None): the block has a mixer only."""
     mixer: object
     feed_forward: object
     mixer_norm: NormSpec
-    feed_forward_norm: NormSpec
+    feed_forward_norm: Optional[NormSpec]
     arrangement: str = "pre_norm"
 
 

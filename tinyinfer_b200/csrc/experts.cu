@@ -1,0 +1,298 @@
+// A feed-forward made of many small experts, of which every token runs a few chosen by a router.
+//   route    : z = W_router x in float32 from the float32 residual row, s = softmax(z) over all experts, the `top`
+//              largest s (first index on ties), weights s_k / (sum of the chosen + weight_eps); also counts the tokens of
+//              every expert and gives each (token, choice) its rank among them
+//   plan     : one block: where every expert's rows start in the sorted order, and the list of row tiles
+//              [expert, first row, rows] that the grouped product walks
+//   place    : slot of every (token, choice) in the sorted order and the token of every slot
+//   grouped product : for every tile, rows x W[expert]^T with float32 FMA accumulation in a fixed k order; the up
+//              form gathers its rows from the tokens and applies max(v, 0)^2, the down form reads the sorted rows
+//   combine_norm_add : y = sum_k weight_k * down[slot_k] (+ the shared expert's output), in choice order, then the
+//              residual x32 += w * y * rsqrt(mean(y^2) + eps) and its copy in the compute dtype
+// A token's result depends on its own row alone: no capacity, nothing dropped, whatever else is in the batch.
+// Nothing here reads back to the host: grids are sized for the worst case and tiles beyond the plan's count return.
+#include "common.cuh"
+
+constexpr int EX_MAX_TOP = 16;
+
+// ------------------------------------------------------------------ route
+// One warp per token. Scores of up to 32 * EX_PER_LANE experts are held a lane apiece.
+constexpr int EX_PER_LANE = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(128) moe_route_kernel(
+    int* __restrict__ chosen, float* __restrict__ weight, int* __restrict__ rank, int* __restrict__ counts,
+    const float* __restrict__ x32, const T* __restrict__ w_router, int num_tokens, int hidden, int experts, int top,
+    float weight_eps) {
+    ti_grid_launch_dependents();
+    ti_grid_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + warp;
+    if (t >= num_tokens) return;
+    const float* x = x32 + (size_t)t * hidden;
+    float z[EX_PER_LANE];                              // lane holds experts lane, lane + 32, ...
+#pragma unroll
+    for (int k = 0; k < EX_PER_LANE; ++k) z[k] = -INFINITY;
+    for (int e = 0; e < experts; ++e) {
+        const T* w = w_router + (size_t)e * hidden;
+        float dot = 0.f;
+        for (int i = lane; i < hidden; i += 32) dot = fmaf(x[i], to_f32(w[i]), dot);
+        dot = warp_sum(dot);
+#pragma unroll
+        for (int k = 0; k < EX_PER_LANE; ++k)
+            if ((e >> 5) == k && (e & 31) == lane) z[k] = dot;
+    }
+    float mx = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < EX_PER_LANE; ++k) mx = fmaxf(mx, z[k]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    float s[EX_PER_LANE];
+#pragma unroll
+    for (int k = 0; k < EX_PER_LANE; ++k) {
+        s[k] = (z[k] == -INFINITY) ? -1.f : expf(z[k] - mx);     // -1 marks "no such expert" (scores are > 0)
+        if (s[k] > 0.f) sum += s[k];
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.f / sum;
+#pragma unroll
+    for (int k = 0; k < EX_PER_LANE; ++k) if (s[k] >= 0.f) s[k] *= inv;
+    float best[EX_MAX_TOP];
+    int who[EX_MAX_TOP];
+    float total = 0.f;
+    for (int c = 0; c < top; ++c) {
+        float v = -1.f;
+        int idx = 0x7fffffff;
+#pragma unroll
+        for (int k = 0; k < EX_PER_LANE; ++k)
+            if (s[k] > v) { v = s[k]; idx = k * 32 + lane; }         // ascending index within a lane: the first wins
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+        }
+        best[c] = v;
+        who[c] = idx;
+        total += v;
+#pragma unroll
+        for (int k = 0; k < EX_PER_LANE; ++k)
+            if (idx == k * 32 + lane) s[k] = -1.f;
+    }
+    if (lane == 0) {
+        const float norm = 1.f / (total + weight_eps);
+        for (int c = 0; c < top; ++c) {
+            chosen[(size_t)t * top + c] = who[c];
+            weight[(size_t)t * top + c] = best[c] * norm;
+            rank[(size_t)t * top + c] = atomicAdd(counts + who[c], 1);
+        }
+    }
+}
+
+// ------------------------------------------------------------------ plan
+// counts[e] -> starts[e] (exclusive sums, starts[experts] = all rows) and tiles [expert, first row, rows];
+// num_tiles[0] = how many. One block; experts and tiles are few.
+__global__ void moe_plan_kernel(int* __restrict__ starts, int* __restrict__ tiles, int* __restrict__ num_tiles,
+                                const int* __restrict__ counts, int experts, int tile_rows, int max_tiles) {
+    ti_grid_launch_dependents();
+    ti_grid_wait();
+    if (threadIdx.x != 0) return;
+    int row = 0, n = 0;
+    for (int e = 0; e < experts; ++e) {
+        starts[e] = row;
+        const int c = counts[e];
+        for (int r = 0; r < c && n < max_tiles; r += tile_rows) {
+            tiles[3 * n] = e;
+            tiles[3 * n + 1] = row + r;
+            tiles[3 * n + 2] = min(tile_rows, c - r);
+            ++n;
+        }
+        row += c;
+    }
+    starts[experts] = row;
+    num_tiles[0] = n;
+}
+
+__global__ void moe_place_kernel(int* __restrict__ slot_of, int* __restrict__ token_of, const int* __restrict__ chosen,
+                                 const int* __restrict__ rank, const int* __restrict__ starts, int n, int top) {
+    ti_grid_launch_dependents();
+    ti_grid_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int slot = starts[chosen[i]] + rank[i];
+    slot_of[i] = slot;
+    token_of[slot] = i / top;
+}
+
+// counts (experts ints) must be zero on entry; the launcher clears them.
+TI_API int ti_moe_route(int* chosen, float* weight, int* rank, int* counts, int* starts, int* tiles, int* num_tiles,
+                        int* slot_of, int* token_of, const float* x32, const void* w_router, int num_tokens, int hidden,
+                        int experts, int top, float weight_eps, int tile_rows, int max_tiles, int dtype, cudaStream_t stream) {
+    TI_REQUIRE(num_tokens >= 0 && hidden > 0 && experts > 0 && top > 0, "moe_route: bad sizes");
+    TI_REQUIRE(top <= EX_MAX_TOP && top <= experts, "moe_route: top %d of %d experts (at most %d)", top, experts, EX_MAX_TOP);
+    TI_REQUIRE(experts <= 32 * EX_PER_LANE, "moe_route: more than %d experts", 32 * EX_PER_LANE);
+    if (num_tokens == 0) return 0;
+    cudaError_t e = cudaMemsetAsync(counts, 0, sizeof(int) * experts, stream);
+    TI_REQUIRE(e == cudaSuccess, "moe_route: %s", cudaGetErrorString(e));
+    const int blocks = (num_tokens + 3) / 4;
+    if (dtype == TI_F32)
+        ti_launch(moe_route_kernel<float>, blocks, 128, 0, stream, chosen, weight, rank, counts, x32, (const float*)w_router,
+                  num_tokens, hidden, experts, top, weight_eps);
+    else if (dtype == TI_BF16)
+        ti_launch(moe_route_kernel<__nv_bfloat16>, blocks, 128, 0, stream, chosen, weight, rank, counts, x32,
+                  (const __nv_bfloat16*)w_router, num_tokens, hidden, experts, top, weight_eps);
+    else TI_REQUIRE(false, "moe_route: unknown dtype %d", dtype);
+    TI_CHECK_LAUNCH("moe_route");
+    ti_launch(moe_plan_kernel, 1, 32, 0, stream, starts, tiles, num_tiles, (const int*)counts, experts, tile_rows, max_tiles);
+    TI_CHECK_LAUNCH("moe_plan");
+    const int n = num_tokens * top;
+    ti_launch(moe_place_kernel, (n + 127) / 128, 128, 0, stream, slot_of, token_of, (const int*)chosen, (const int*)rank,
+              (const int*)starts, n, top);
+    TI_CHECK_LAUNCH("moe_place");
+    return 0;
+}
+
+// ------------------------------------------------------------------ grouped product
+constexpr int EG_BM = 32, EG_BN = 64, EG_BK = 16, EG_THREADS = 128;
+
+// out[row][n] = act(sum_k x[src(row)][k] * w[expert][n][k]) for the rows of tile blockIdx.y.
+// GATHER: src(row) = token_of[row] (rows of the step's tokens); else src(row) = row (sorted rows).
+template <typename T, typename OutT, bool GATHER, bool RELU2>
+__global__ void __launch_bounds__(EG_THREADS) moe_gemm_kernel(
+    OutT* __restrict__ out, const T* __restrict__ x, const T* __restrict__ w, const int* __restrict__ tiles,
+    const int* __restrict__ num_tiles, const int* __restrict__ token_of, int N, int K) {
+    __shared__ float As[EG_BK][EG_BM + 4];
+    __shared__ float Bs[EG_BK][EG_BN + 4];
+    __shared__ int src[EG_BM];
+    ti_grid_launch_dependents();
+    ti_grid_wait();
+    if ((int)blockIdx.y >= num_tiles[0]) return;
+    const int expert = tiles[3 * blockIdx.y], row0 = tiles[3 * blockIdx.y + 1], rows = tiles[3 * blockIdx.y + 2];
+    const int tid = threadIdx.x;
+    const int tx = tid & 15, ty = tid >> 4;             // 16 x 8 threads, 4 x 4 outputs each
+    const int n0 = blockIdx.x * EG_BN;
+    const T* we = w + (size_t)expert * N * K;
+    if (tid < EG_BM) src[tid] = tid < rows ? (GATHER ? token_of[row0 + tid] : row0 + tid) : -1;
+    __syncthreads();
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < K; k0 += EG_BK) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {                   // 32 x 16 of x
+            const int idx = tid + r * EG_THREADS;
+            const int row = idx >> 4, col = idx & 15;
+            const int k = k0 + col;
+            const int s = src[row];
+            As[col][row] = (s >= 0 && k < K) ? to_f32(x[(size_t)s * K + k]) : 0.f;
+        }
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {                   // 64 x 16 of w
+            const int idx = tid + r * EG_THREADS;
+            const int row = idx >> 4, col = idx & 15;
+            const int k = k0 + col, n = n0 + row;
+            Bs[col][row] = (n < N && k < K) ? to_f32(we[(size_t)n * K + k]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < EG_BK; ++kk) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) b[j] = Bs[kk][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = ty * 4 + i;
+        if (r >= rows) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= N) continue;
+            float v = acc[i][j];
+            if (RELU2) { v = fmaxf(v, 0.f); v *= v; }
+            out[(size_t)(row0 + r) * N + n] = from_f32<OutT>(v);
+        }
+    }
+}
+
+TI_API int ti_moe_tile_rows() { return EG_BM; }
+
+// up != 0: x [tokens, K] gathered through token_of, out [slots, N] in the compute dtype after max(v, 0)^2;
+// else x [slots, K], out [slots, N] float32. w [experts, N, K]. max_tiles: the grid's height.
+TI_API int ti_moe_gemm(void* out, const void* x, const void* w, const int* tiles, const int* num_tiles, const int* token_of,
+                       int N, int K, int max_tiles, int up, int dtype, cudaStream_t stream) {
+    TI_REQUIRE(N > 0 && K > 0 && max_tiles >= 0 && max_tiles <= 65535, "moe_gemm: bad sizes");
+    if (max_tiles == 0) return 0;
+    dim3 grid((N + EG_BN - 1) / EG_BN, max_tiles);
+    typedef __nv_bfloat16 B;
+    if (dtype == TI_F32) {
+        if (up) ti_launch(moe_gemm_kernel<float, float, true, true>, grid, EG_THREADS, 0, stream, (float*)out, (const float*)x, (const float*)w, tiles, num_tiles, token_of, N, K);
+        else ti_launch(moe_gemm_kernel<float, float, false, false>, grid, EG_THREADS, 0, stream, (float*)out, (const float*)x, (const float*)w, tiles, num_tiles, token_of, N, K);
+    } else if (dtype == TI_BF16) {
+        if (up) ti_launch(moe_gemm_kernel<B, B, true, true>, grid, EG_THREADS, 0, stream, (B*)out, (const B*)x, (const B*)w, tiles, num_tiles, token_of, N, K);
+        else ti_launch(moe_gemm_kernel<B, float, false, false>, grid, EG_THREADS, 0, stream, (float*)out, (const B*)x, (const B*)w, tiles, num_tiles, token_of, N, K);
+    } else TI_REQUIRE(false, "moe_gemm: unknown dtype %d", dtype);
+    TI_CHECK_LAUNCH("moe_gemm");
+    return 0;
+}
+
+// ------------------------------------------------------------------ combine + norm + residual
+template <typename T>
+__global__ void moe_combine_norm_add_kernel(float* __restrict__ x32, T* __restrict__ copy, const float* __restrict__ down,
+                                            const T* __restrict__ shared_out, const int* __restrict__ slot_of,
+                                            const float* __restrict__ weight, const float* __restrict__ norm_w, int size,
+                                            int top, float eps) {
+    extern __shared__ float row[];
+    __shared__ float red[33];
+    __shared__ int slots[EX_MAX_TOP];
+    __shared__ float wts[EX_MAX_TOP];
+    ti_grid_launch_dependents();
+    ti_grid_wait();
+    const int t = blockIdx.x;
+    if (threadIdx.x < top) {
+        slots[threadIdx.x] = slot_of[(size_t)t * top + threadIdx.x];
+        wts[threadIdx.x] = weight[(size_t)t * top + threadIdx.x];
+    }
+    __syncthreads();
+    const size_t base = (size_t)t * size;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < size; i += blockDim.x) {
+        float v = 0.f;
+        for (int c = 0; c < top; ++c) v = fmaf(wts[c], down[(size_t)slots[c] * size + i], v);
+        if (shared_out) v += to_f32(shared_out[base + i]);
+        row[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)size + eps);
+    for (int i = threadIdx.x; i < size; i += blockDim.x) {
+        const float v = x32[base + i] + norm_w[i] * row[i] * inv;
+        x32[base + i] = v;
+        if (copy) copy[base + i] = from_f32<T>(v);
+    }
+}
+
+TI_API int ti_moe_combine_norm_add(float* x32, void* copy, const float* down, const void* shared_out, const int* slot_of,
+                                   const float* weight, const float* norm_w, int num_tokens, int size, int top, float eps,
+                                   int dtype, cudaStream_t stream) {
+    TI_REQUIRE(num_tokens >= 0 && size > 0 && size <= 48 * 1024 / 4 && top > 0 && top <= EX_MAX_TOP, "moe_combine: bad sizes");
+    if (num_tokens == 0) return 0;
+    int threads = 32;
+    while (threads < 512 && threads * 4 < size) threads <<= 1;
+    const size_t smem = (size_t)size * 4;
+    if (dtype == TI_F32)
+        ti_launch(moe_combine_norm_add_kernel<float>, num_tokens, threads, smem, stream, x32, (float*)copy, down,
+                  (const float*)shared_out, slot_of, weight, norm_w, size, top, eps);
+    else if (dtype == TI_BF16)
+        ti_launch(moe_combine_norm_add_kernel<__nv_bfloat16>, num_tokens, threads, smem, stream, x32, (__nv_bfloat16*)copy, down,
+                  (const __nv_bfloat16*)shared_out, slot_of, weight, norm_w, size, top, eps);
+    else TI_REQUIRE(false, "moe_combine: unknown dtype %d", dtype);
+    TI_CHECK_LAUNCH("moe_combine_norm_add");
+    return 0;
+}

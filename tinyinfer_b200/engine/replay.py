@@ -37,9 +37,10 @@ class TraceSession:
             require_cuda(device)
             model, _ = load_model(model_dir, dtype, device)
         self.model = model
-        limit = model.spec.max_positions
+        pages = pool_pages(max_tokens, page_size)
+        limit = min(model.spec.max_positions, pages * page_size)     # no request can outgrow the pool
         self.runner = ModelRunner(
-            model, page_size=page_size, num_pages=pool_pages(max_tokens, page_size),
+            model, page_size=page_size, num_pages=pages,
             max_requests=max_live, max_tokens_per_step=max(max_tokens, 1), max_model_len=limit,
             poison_cache=poison_cache, cuda_graphs=cuda_graphs)
 

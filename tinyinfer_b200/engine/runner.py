@@ -40,7 +40,8 @@ class ModelRunner:
                                     max(1, len(self.manager.groups)))
         self.steps_run = 0
         self.cuda_graphs = (cuda_graphs and self.device.type == "cuda"
-                            and all(b.mixer.graph_safe and b.feed_forward.graph_safe for b in model.blocks))
+                            and all(b.mixer.graph_safe and (b.feed_forward is None or b.feed_forward.graph_safe)
+                                    for b in model.blocks))
         self._tables_only_grow = all(g.need.window is None for g in self.manager.groups)
         self._graphs = {}          # requests in the step -> (graph, static logits, kernels)
         self._graph_pool = None
@@ -175,6 +176,8 @@ class ModelRunner:
         self.storage.state.clear()
         for block in self.model.blocks:
             for part in (block.mixer, block.feed_forward, block.mixer_norm, block.feed_forward_norm):
+                if part is None:
+                    continue
                 for name, value in list(vars(part).items()):
                     if isinstance(value, torch.Tensor):
                         setattr(part, name, None)

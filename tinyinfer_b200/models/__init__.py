@@ -1,4 +1,5 @@
 from .decoder import DecoderModel
+from .gulisun import GulisunForCausalLM
 from .qwen3 import Qwen3ForCausalLM
 
-__all__ = ["DecoderModel", "Qwen3ForCausalLM"]
+__all__ = ["DecoderModel", "GulisunForCausalLM", "Qwen3ForCausalLM"]

@@ -35,9 +35,10 @@ class DecoderModel:
         n = self.spec.names
         base = n.layer.format(i=i)
         block = self.blocks[i]
-        return [(base + n.mixer, block.mixer), (base + n.feed_forward, block.feed_forward),
-                (base + n.mixer_norm, block.mixer_norm),
-                (base + n.feed_forward_norm, block.feed_forward_norm)]
+        parts = [(base + n.mixer, block.mixer), (base + n.feed_forward, block.feed_forward),
+                 (base + n.mixer_norm, block.mixer_norm),
+                 (base + n.feed_forward_norm, block.feed_forward_norm)]
+        return [(prefix, part) for prefix, part in parts if part is not None]     # a block may have a mixer only
 
     def expected_tensors(self) -> Dict[str, TensorSpec]:
         """Checkpoint name -> what the tensor must look like, in a fixed order."""

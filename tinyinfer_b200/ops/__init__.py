@@ -45,6 +45,30 @@ _SIGNATURES = {
         "ti_token_nll": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
         "ti_sample_parts": [],
         "ti_sample_candidates": [],
+        "ti_embedding_scaled": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p],
+        "ti_norm_add": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p],
+        "ti_rmsnorm_rows32": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
+        "ti_relu_squared": [c_void_p, c_void_p, c_ll, c_int, c_void_p],
+        "ti_gemm_batched": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_ll,
+                            c_ll, c_ll, c_ll, c_int, c_int, c_int, c_void_p],
+        "ti_latent_prepare": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_int,
+                              c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                              c_int, c_void_p, c_int, c_void_p],
+        "ti_latent_query": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                            c_void_p, c_int, c_void_p],
+        "ti_latent_attend": [c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                             c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_int, c_void_p],
+        "ti_causal_conv": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                           c_int, c_int, c_int, c_int, c_void_p],
+        "ti_gated_scan": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
+                          c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+        "ti_moe_route": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                         c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p],
+        "ti_moe_tile_rows": [],
+        "ti_moe_gemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                        c_void_p],
+        "ti_moe_combine_norm_add": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                    c_int, c_float, c_int, c_void_p],
     },
 }
 _SIGNATURES["sm100"] = {
@@ -629,6 +653,310 @@ def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, *, positions: torch
     if num_tiles > num_pairs:                       # ends of portions of at most 128 rows
         one_tile_kernel(num_pairs, num_tiles - num_pairs, 0)
     return out
+
+
+# ---------------------------------------------------------------------- a float32 residual stream
+def embedding_scaled(token_ids: torch.Tensor, table: torch.Tensor, scale: float):
+    """(x32, copy): float32 rows ``table[token_ids] * scale`` and their rounding in the table's dtype
+    (``copy`` is x32 itself for a float32 table)."""
+    _check(token_ids, "token_ids", torch.int32, 1)
+    _check(table, "table", None, 2)
+    t, hidden = token_ids.shape[0], table.shape[1]
+    x32 = torch.empty((t, hidden), dtype=torch.float32, device=table.device)
+    copy = None if table.dtype == torch.float32 else torch.empty((t, hidden), dtype=table.dtype, device=table.device)
+    _run("core", "ti_embedding_scaled", x32.data_ptr(), _ptr(copy), table.data_ptr(), token_ids.data_ptr(), t, hidden,
+         table.shape[0], float(scale), _dtype_code(table), _stream())
+    return x32, (x32 if copy is None else copy)
+
+
+def norm_add(x32: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, copy_dtype: torch.dtype):
+    """x32 += weight * y * rsqrt(mean(y^2) + eps) in place (float32 [T, size]); returns (x32, copy) with the
+    rounding of the new rows in ``copy_dtype`` (x32 itself for float32). ``y``: float32 or ``copy_dtype``."""
+    _check(x32, "x32", torch.float32, 2)
+    _check(y, "y", None, 2)
+    _check(weight, "weight", torch.float32, 1)
+    if y.shape != x32.shape or weight.shape[0] != x32.shape[1]:
+        raise KernelError("norm_add: shapes differ")
+    if y.dtype not in (torch.float32, copy_dtype):
+        raise KernelError(f"norm_add: y is {y.dtype}, the stream's copy {copy_dtype}")
+    copy = None if copy_dtype == torch.float32 else torch.empty(x32.shape, dtype=copy_dtype, device=x32.device)
+    _run("core", "ti_norm_add", x32.data_ptr(), _ptr(copy), y.data_ptr(), weight.data_ptr(), x32.shape[0], x32.shape[1],
+         float(eps), _dtype_code(y), 0 if copy is None else _dtype_code(copy), _stream())
+    return x32, (x32 if copy is None else copy)
+
+
+def rmsnorm_rows32(x32: torch.Tensor, weight: torch.Tensor, eps: float, rows: Optional[torch.Tensor],
+                   out_dtype: torch.dtype) -> torch.Tensor:
+    """RMSNorm of float32 rows (all, or those ``rows`` int32 [N] picks), stored in ``out_dtype``."""
+    _check(x32, "x32", torch.float32, 2)
+    _check(weight, "weight", torch.float32, 1)
+    if rows is not None:
+        _check(rows, "rows", torch.int32, 1)
+    n = x32.shape[0] if rows is None else rows.shape[0]
+    out = torch.empty((n, x32.shape[1]), dtype=out_dtype, device=x32.device)
+    _run("core", "ti_rmsnorm_rows32", out.data_ptr(), x32.data_ptr(), weight.data_ptr(), _ptr(rows), n, x32.shape[1],
+         float(eps), _dtype_code(out), _stream())
+    return out
+
+
+def relu_squared(x: torch.Tensor) -> torch.Tensor:
+    """max(x, 0)^2, one rounding."""
+    _check(x, "x")
+    out = torch.empty_like(x)
+    _run("core", "ti_relu_squared", out.data_ptr(), x.data_ptr(), x.numel(), _dtype_code(x), _stream())
+    return out
+
+
+def batched_linear(x: torch.Tensor, w: torch.Tensor, *, x_offset: int = 0, x_batch_stride: int, k: int,
+                   out: Optional[torch.Tensor] = None, out_offset: int = 0, out_batch_stride: Optional[int] = None,
+                   bias: Optional[torch.Tensor] = None, sigmoid: bool = False, out_float32: bool = False) -> torch.Tensor:
+    """For every batch b of ``w`` [B, N, K]: out[:, b-th piece] = act(x[:, b-th piece] . w[b]^T + bias[b]).
+    ``x`` [M, row] holds the batches side by side in each row: piece b starts at column
+    ``x_offset + b * x_batch_stride`` and has ``k`` columns; likewise ``out`` [M, row_out] (made here as
+    [M, B * N] if not given) with ``out_offset`` and ``out_batch_stride`` (default N). float32 accumulation."""
+    _check(x, "x", None, 2)
+    _check(w, "w", x.dtype, 3)
+    batch, n, kw = w.shape
+    if kw != k:
+        raise KernelError(f"batched_linear: w has {kw} columns, the pieces of x {k}")
+    m = x.shape[0]
+    if x_offset + (batch - 1) * x_batch_stride + k > x.shape[1]:
+        raise KernelError("batched_linear: the pieces do not fit the rows of x")
+    if out_batch_stride is None:
+        out_batch_stride = n
+    if out is None:
+        out = torch.empty((m, out_offset + batch * out_batch_stride), device=x.device,
+                          dtype=torch.float32 if out_float32 else x.dtype)
+    _check(out, "out", None, 2)
+    if out.dtype not in (torch.float32, x.dtype):
+        raise KernelError(f"batched_linear: out must be float32 or {x.dtype}, got {out.dtype}")
+    if out.shape[0] != m or out_offset + (batch - 1) * out_batch_stride + n > out.shape[1]:
+        raise KernelError("batched_linear: the pieces do not fit the rows of out")
+    if bias is not None:
+        _check(bias, "bias", torch.float32, 2)
+        if tuple(bias.shape) != (batch, n):
+            raise KernelError("batched_linear: bias must be [B, N]")
+    isz_x, isz_o = x.element_size(), out.element_size()
+    _run("core", "ti_gemm_batched", out.data_ptr() + out_offset * isz_o, x.data_ptr() + x_offset * isz_x, w.data_ptr(),
+         _ptr(bias), batch, m, n, k, x.shape[1], x_batch_stride, k, n * k, out.shape[1], out_batch_stride, n,
+         int(sigmoid), int(out.dtype == torch.float32 and x.dtype != torch.float32), _dtype_code(x), _stream())
+    return out
+
+
+# ---------------------------------------------------------------------- attention over a cached latent
+def _rotation_args(rot: Optional[Rotation]):
+    if rot is None:
+        return None, None, 0, 0, 0
+    _check(rot.inv_freq if rot.inv_freq is not None else rot.cos_sin, "the rotation's tensor")
+    return (_ptr(rot.inv_freq), _ptr(rot.cos_sin), rot.cos_sin.shape[0] if rot.cos_sin is not None else 0,
+            int(rot.interleaved), rot.rotary_dim)
+
+
+def latent_prepare(down: torch.Tensor, *, q_rank: int, rank: int, rot: int, q_norm_weight: torch.Tensor,
+                   kv_norm_weight: Optional[torch.Tensor], eps: float, rotation: Optional[Rotation],
+                   positions: torch.Tensor, token_seq: torch.Tensor, cache: Optional[torch.Tensor],
+                   block_table: torch.Tensor, dtype: torch.dtype, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``down`` float32 [T, q_rank (+ rank + rot)]: a token's down projections [query latent | kv latent | keys to
+    rotate]. Returns the normed query latent [T, q_rank] in ``dtype`` and, if ``cache`` ([1, pages, 1, page,
+    rank + rot], ``dtype``) is given, writes the token's row [normed kv latent | rotated keys] there."""
+    _check(down, "down", torch.float32, 2)
+    _check(q_norm_weight, "q_norm_weight", torch.float32, 1)
+    _check(positions, "positions", torch.int32, 1)
+    _check(token_seq, "token_seq", torch.int32, 1)
+    t = down.shape[0]
+    need = q_rank + (rank + rot if cache is not None else 0)
+    if down.shape[1] < need:
+        raise KernelError(f"latent_prepare: rows of {down.shape[1]} features, {need} are needed")
+    page_size = num_pages = 1
+    max_blocks = 0
+    if cache is not None:
+        _check(cache, "cache", dtype, 5)
+        _check(kv_norm_weight, "kv_norm_weight", torch.float32, 1)
+        _check(block_table, "block_table", torch.int32, 2)
+        if cache.shape[0] != 1 or cache.shape[2] != 1 or cache.shape[4] != rank + rot:
+            raise KernelError(f"latent cache shape {tuple(cache.shape)} is not [1, pages, 1, page, {rank + rot}]")
+        num_pages, page_size, max_blocks = cache.shape[1], cache.shape[3], block_table.shape[1]
+    out = torch.empty((t, q_rank), dtype=dtype, device=down.device)
+    _run("core", "ti_latent_prepare", out.data_ptr(), _ptr(cache), down.data_ptr(), down.shape[1],
+         q_norm_weight.data_ptr(), _ptr(kv_norm_weight), float(eps), q_rank, rank, rot, *_rotation_args(rotation),
+         positions.data_ptr(), token_seq.data_ptr(), _ptr(block_table) if cache is not None else None, max_blocks, t,
+         page_size, num_pages, _ptr(status), _dtype_code(out), _stream())
+    return out
+
+
+def latent_query_rotate(rows: torch.Tensor, q: torch.Tensor, *, heads: int, plain: int, rot: int, rank: int,
+                        rotation: Optional[Rotation], positions: torch.Tensor) -> None:
+    """Writes the rotated last ``rot`` features of every head of ``q`` [T, heads * (plain + rot)] into
+    ``rows`` float32 [T, heads * (rank + rot)], behind each head's first ``rank`` features."""
+    _check(rows, "rows", torch.float32, 2)
+    _check(q, "q", None, 2)
+    _check(positions, "positions", torch.int32, 1)
+    if q.shape[1] != heads * (plain + rot) or rows.shape[1] != heads * (rank + rot) or rows.shape[0] != q.shape[0]:
+        raise KernelError("latent_query_rotate: widths do not match the head sizes")
+    _run("core", "ti_latent_query", rows.data_ptr(), q.data_ptr(), q.shape[0], heads, plain, rot, rank,
+         *_rotation_args(rotation), positions.data_ptr(), _dtype_code(q), _stream())
+
+
+LATENT_SPLIT_MIN_KEYS = 256     # a split of the keys over blocks gets at least this many
+LATENT_TARGET_BLOCKS = 296      # enough blocks to have two on every SM
+
+
+def latent_attention(q_rows: torch.Tensor, cache: torch.Tensor, *, heads: int, rank: int, rot: int, scale: float,
+                     sink: Optional[torch.Tensor], positions: torch.Tensor, token_seq: torch.Tensor,
+                     block_table: torch.Tensor, max_context: int, window: Optional[int] = None,
+                     status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention of query rows float32 [T, heads * (rank + rot)] over each token's own request's cached
+    rows [c | k_rot] (``cache`` [1, pages, 1, page, rank + rot]); returns sum_j p_j c_j per head, [T, heads * rank]
+    in the cache's dtype. ``sink`` float32 [heads]: exp(sink) joins every softmax denominator. ``max_context``
+    (a host number, the longest context of the step) only decides over how many blocks the keys are shared."""
+    _check(q_rows, "q_rows", torch.float32, 2)
+    _check(cache, "cache", None, 5)
+    _check(positions, "positions", torch.int32, 1)
+    _check(token_seq, "token_seq", torch.int32, 1)
+    _check(block_table, "block_table", torch.int32, 2)
+    if sink is not None:
+        _check(sink, "sink", torch.float32, 1)
+        if sink.shape[0] != heads:
+            raise KernelError("latent_attention: one sink per head")
+    t = q_rows.shape[0]
+    if q_rows.shape[1] != heads * (rank + rot) or cache.shape[4] != rank + rot or cache.shape[0] != 1 or cache.shape[2] != 1:
+        raise KernelError("latent_attention: the query rows or the cache do not match rank and rot")
+    out = torch.empty((t, heads * rank), dtype=cache.dtype, device=cache.device)
+    if t == 0:
+        return out
+    blocks = t * ((heads + 7) // 8)
+    splits = 1
+    if blocks < LATENT_TARGET_BLOCKS and max_context >= 2 * LATENT_SPLIT_MIN_KEYS:
+        splits = max(1, min(-(-LATENT_TARGET_BLOCKS // blocks), int(max_context) // LATENT_SPLIT_MIN_KEYS, 64))
+    parts, parts_floats = None, 0
+    if splits > 1:
+        parts = _decode_scratch(cache.device, t * heads * splits * (rank + 2))
+        parts_floats = parts.numel()
+    _run("core", "ti_latent_attend", out.data_ptr(), _ptr(parts), parts_floats, q_rows.data_ptr(), cache.data_ptr(),
+         _ptr(sink), positions.data_ptr(), token_seq.data_ptr(), block_table.data_ptr(), block_table.shape[1], t, heads,
+         rank, rot, cache.shape[3], cache.shape[1], float(scale), int(window or 0), splits, _ptr(status),
+         _dtype_code(cache), _stream())
+    return out
+
+
+# ---------------------------------------------------------------------- gated linear recurrence
+def causal_conv(x: torch.Tensor, *, offset: int, width: int, state: torch.Tensor, weight: torch.Tensor,
+                bias: Optional[torch.Tensor], token_seq: torch.Tensor, cu_seqlens: torch.Tensor,
+                state_slots: torch.Tensor) -> torch.Tensor:
+    """Per-channel causal convolution of columns [offset, offset + width) of ``x`` [T, row]: ``weight`` float32
+    [width, taps], last column the current token's. Inputs from before the step come from ``state`` float32
+    [slots, taps, width] (rows 1.. of a slot: the last taps - 1 inputs, oldest first). Returns [T, width]."""
+    _check(x, "x", None, 2)
+    _check(state, "state", torch.float32, 3)
+    _check(weight, "weight", torch.float32, 2)
+    taps = weight.shape[1]
+    if weight.shape[0] != width or state.shape[1] != taps or state.shape[2] != width or offset + width > x.shape[1]:
+        raise KernelError("causal_conv: shapes do not match")
+    if bias is not None:
+        _check(bias, "bias", torch.float32, 1)
+    out = torch.empty((x.shape[0], width), dtype=x.dtype, device=x.device)
+    _run("core", "ti_causal_conv", out.data_ptr(), x.data_ptr(), x.shape[1], offset, state.data_ptr(), weight.data_ptr(),
+         _ptr(bias), token_seq.data_ptr(), cu_seqlens.data_ptr(), state_slots.data_ptr(), x.shape[0], width, taps,
+         _dtype_code(x), _stream())
+    return out
+
+
+def gated_scan(u: torch.Tensor, gates: torch.Tensor, yx: torch.Tensor, *, y_offset: int, x_offset: int,
+               state: torch.Tensor, lam: torch.Tensor, block_width: int, decay: float, cu_seqlens: torch.Tensor,
+               state_slots: torch.Tensor, num_seqs: int) -> torch.Tensor:
+    """The recurrence S <- a S + sqrt(1 - a^2) (i u), a = exp(-decay r softplus(lam)), over every request's tokens
+    of the step in order, from and back into ``state`` float32 [slots, taps, width] (row 0: S; the rows behind it
+    take the convolution's newest inputs, columns [x_offset, +width) of ``yx``). ``gates`` float32 [T, 2 width],
+    per block [r | i]. Returns S * gelu_tanh(y) with y = columns [y_offset, +width) of ``yx``, [T, width]."""
+    _check(u, "u", None, 2)
+    _check(gates, "gates", torch.float32, 2)
+    _check(yx, "yx", u.dtype, 2)
+    _check(state, "state", torch.float32, 3)
+    _check(lam, "lam", torch.float32, 1)
+    t, width = u.shape
+    if gates.shape != (t, 2 * width) or yx.shape[0] != t or state.shape[2] != width or lam.shape[0] != width:
+        raise KernelError("gated_scan: shapes do not match")
+    out = torch.empty((t, width), dtype=u.dtype, device=u.device)
+    _run("core", "ti_gated_scan", out.data_ptr(), state.data_ptr(), u.data_ptr(), gates.data_ptr(), yx.data_ptr(),
+         yx.shape[1], y_offset, x_offset, lam.data_ptr(), cu_seqlens.data_ptr(), state_slots.data_ptr(), num_seqs, width,
+         block_width, state.shape[1], float(decay), _dtype_code(u), _stream())
+    return out
+
+
+# ---------------------------------------------------------------------- routed experts
+class ExpertRouting:
+    """Where a step's tokens go: ``chosen`` int32 [T, top], ``weight`` float32 [T, top], ``slot_of`` int32 [T, top]
+    (row of each (token, choice) in the order sorted by expert), ``token_of`` int32 [T * top], and the row tiles
+    ``tiles`` int32 [max_tiles, 3] = [expert, first row, rows] with their count ``num_tiles`` int32 [1] (on the
+    device: the grouped products are launched for ``max_tiles`` and the surplus returns at once)."""
+
+    def __init__(self, chosen, weight, slot_of, token_of, tiles, num_tiles, max_tiles, counts):
+        self.chosen, self.weight, self.slot_of, self.token_of = chosen, weight, slot_of, token_of
+        self.tiles, self.num_tiles, self.max_tiles, self.counts = tiles, num_tiles, max_tiles, counts
+
+
+def route_experts(x32: torch.Tensor, w_router: torch.Tensor, top: int, weight_eps: float) -> ExpertRouting:
+    """Router of a mixture of experts: float32 logits from the float32 rows ``x32`` [T, H] and ``w_router`` [E, H],
+    softmax over all experts, the ``top`` largest (first index on ties), weights = their scores over their sum
+    (+ ``weight_eps``)."""
+    _check(x32, "x32", torch.float32, 2)
+    _check(w_router, "w_router", None, 2)
+    t, hidden = x32.shape
+    experts = w_router.shape[0]
+    if w_router.shape[1] != hidden:
+        raise KernelError("route_experts: the router's rows do not match the stream's")
+    dev = x32.device
+    fn = _fn("core", "ti_moe_tile_rows")
+    tile_rows = int(fn())
+    max_tiles = (t * top + tile_rows - 1) // tile_rows + experts
+    ints = torch.empty(t * top * 4 + experts + (experts + 1) + 3 * max_tiles + 1, dtype=torch.int32, device=dev)
+    n = t * top
+    chosen, rank, slot_of, token_of = (ints[i * n:(i + 1) * n] for i in range(4))
+    o = 4 * n
+    counts, starts = ints[o:o + experts], ints[o + experts:o + 2 * experts + 1]
+    o += 2 * experts + 1
+    tiles, num_tiles = ints[o:o + 3 * max_tiles], ints[o + 3 * max_tiles:o + 3 * max_tiles + 1]
+    weight = torch.empty((t, top), dtype=torch.float32, device=dev)
+    _run("core", "ti_moe_route", chosen.data_ptr(), weight.data_ptr(), rank.data_ptr(), counts.data_ptr(),
+         starts.data_ptr(), tiles.data_ptr(), num_tiles.data_ptr(), slot_of.data_ptr(), token_of.data_ptr(),
+         x32.data_ptr(), w_router.data_ptr(), t, hidden, experts, top, float(weight_eps), tile_rows, max_tiles,
+         _dtype_code(w_router), _stream())
+    return ExpertRouting(chosen.view(t, top), weight, slot_of.view(t, top), token_of, tiles.view(max_tiles, 3),
+                         num_tiles, max_tiles, counts)
+
+
+def expert_linear(x: torch.Tensor, w: torch.Tensor, routing: ExpertRouting, *, up: bool) -> torch.Tensor:
+    """Grouped product over the routing's row tiles with ``w`` [E, N, K]. ``up``: ``x`` [T, K] are the step's
+    tokens, gathered per expert; the result [T * top, N] (sorted rows) has passed max(v, 0)^2. Otherwise ``x``
+    are sorted rows [T * top, K] and the result is float32 [T * top, N]."""
+    _check(x, "x", None, 2)
+    _check(w, "w", x.dtype, 3)
+    _, n, k = w.shape
+    if x.shape[1] != k:
+        raise KernelError("expert_linear: x and w do not match")
+    slots = routing.token_of.shape[0]
+    out = torch.empty((slots, n), dtype=x.dtype if up else torch.float32, device=x.device)
+    _run("core", "ti_moe_gemm", out.data_ptr(), x.data_ptr(), w.data_ptr(), routing.tiles.data_ptr(),
+         routing.num_tiles.data_ptr(), routing.token_of.data_ptr(), n, k, routing.max_tiles, int(up), _dtype_code(x),
+         _stream())
+    return out
+
+
+def experts_combine_norm_add(x32: torch.Tensor, down: torch.Tensor, shared_out: Optional[torch.Tensor],
+                             routing: ExpertRouting, norm_weight: torch.Tensor, eps: float, copy_dtype: torch.dtype):
+    """y = sum_k weight_k * down[slot_k] (+ shared_out), then x32 += norm_weight * y * rsqrt(mean(y^2) + eps) in
+    place; returns (x32, copy) as ``norm_add`` does."""
+    _check(x32, "x32", torch.float32, 2)
+    _check(down, "down", torch.float32, 2)
+    _check(norm_weight, "norm_weight", torch.float32, 1)
+    if shared_out is not None:
+        _check(shared_out, "shared_out", copy_dtype, 2)
+    t, size = x32.shape
+    copy = None if copy_dtype == torch.float32 else torch.empty((t, size), dtype=copy_dtype, device=x32.device)
+    _run("core", "ti_moe_combine_norm_add", x32.data_ptr(), _ptr(copy), down.data_ptr(), _ptr(shared_out),
+         routing.slot_of.data_ptr(), routing.weight.data_ptr(), norm_weight.data_ptr(), t, size,
+         routing.chosen.shape[1], float(eps), 0 if copy is None else _dtype_code(copy), _stream())
+    return x32, (x32 if copy is None else copy)
 
 
 # ---------------------------------------------------------------------- sampling

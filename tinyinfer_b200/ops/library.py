@@ -33,7 +33,8 @@ COMMON_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcomp
 LIBRARIES: Dict[str, dict] = {
     # every dtype, every shape: the 32-bit path and the general bfloat16 path
     "core": dict(sources=["runtime.cu", "elementwise.cu", "rope_append.cu",
-                          "attention_generic.cu", "gemm_simt.cu", "sampling.cu"],
+                          "attention_generic.cu", "gemm_simt.cu", "sampling.cu", "stream.cu",
+                          "gemm_batched.cu", "latent_attention.cu", "recurrent.cu", "experts.cu"],
                  headers=["common.cuh"], link=[]),
     # bfloat16 tensor-core kernels (tcgen05 + TMA); only a bfloat16 model loads it
     "sm100": dict(sources=["runtime.cu", "sm100_host.cu", "gemm_tcgen05.cu", "attention_mma.cu",

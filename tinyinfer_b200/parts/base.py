@@ -35,6 +35,7 @@ class CacheNeed:
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    planes: int = 2          # 2: keys and values; 1: one row per token (a latent that both are made from)
 
 
 @dataclass(frozen=True)
@@ -134,7 +135,8 @@ class FeedForward(Part):
 
 
 class Block:
-    """An arrangement of one mixer, one feed-forward and their norms."""
+    """An arrangement of one mixer, one feed-forward and their norms (``feed_forward`` and its norm are None in
+    a block that has a mixer only; an arrangement that allows that says so in its own ``forward``)."""
 
     def __init__(self, spec, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm,
                  feed_forward_norm: Norm):
@@ -194,6 +196,6 @@ def build_block(spec, dtype, device) -> Block:
     return _BLOCKS[spec.arrangement](
         spec,
         build_mixer(spec.mixer, dtype, device),
-        build_feed_forward(spec.feed_forward, dtype, device),
+        build_feed_forward(spec.feed_forward, dtype, device) if spec.feed_forward is not None else None,
         build_norm(spec.mixer_norm, dtype, device),
-        build_norm(spec.feed_forward_norm, dtype, device))
+        build_norm(spec.feed_forward_norm, dtype, device) if spec.feed_forward_norm is not None else None)

@@ -18,4 +18,31 @@ class PreNormBlock(Block):
         return x, link
 
 
+class OutputNormBlock(Block):
+    """x <- x + norm1(mixer(x)); x <- x + norm2(feed_forward(x)): both sublayers read x itself and the norm sits on
+    a sublayer's OUTPUT. The stream is a pair (x32, copy): the residual sums are float32, ``copy`` is their
+    rounding in the compute dtype, which the matrix products read (the same tensor in a float32 model).
+    A block may have no feed-forward."""
+
+    def forward(self, x, step, cache):
+        return self.forward_linked(x, None, None, step, cache)[0]
+
+    def forward_linked(self, x, link, next_norm, step, cache):
+        from .. import ops
+        x32, copy = x
+        rms = self.mixer_norm.as_rms()
+        if rms is None:
+            raise ValueError("the output-norm arrangement needs RMSNorms")
+        mixed = self.mixer.forward(copy, step, cache)
+        x32, copy = ops.norm_add(x32, mixed, rms[0], rms[1], self.mixer.dtype)
+        if self.feed_forward is not None:
+            if hasattr(self.feed_forward, "forward_stream"):
+                x32, copy = self.feed_forward.forward_stream(x32, copy, self.feed_forward_norm, step)
+            else:
+                rms = self.feed_forward_norm.as_rms()
+                x32, copy = ops.norm_add(x32, self.feed_forward.forward(copy, step), rms[0], rms[1], self.mixer.dtype)
+        return (x32, copy), None
+
+
 register_block("pre_norm", PreNormBlock)
+register_block("output_norm", OutputNormBlock)

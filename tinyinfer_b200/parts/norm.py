@@ -13,10 +13,10 @@ class RMSNorm(Norm):
         self.weight = None
 
     def tensors(self):
-        return {"weight": TensorSpec((self.spec.size,), role="vector32", init="ones_noise")}
+        return {self.spec.tensor: TensorSpec((self.spec.size,), role="vector32", init="ones_noise")}
 
     def load(self, tensors):
-        self.weight = tensors["weight"]
+        self.weight = tensors[self.spec.tensor]
 
     def forward(self, x):
         return ops.rmsnorm(x, self.weight, self.spec.eps)

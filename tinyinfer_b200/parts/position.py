@@ -14,8 +14,12 @@ class RotaryEncoding(PositionEncoding):
         super().__init__(spec, dtype, device)
         if spec.rotary_dim <= 0 or spec.rotary_dim % 2:
             raise ValueError(f"rotary_dim must be positive and even, got {spec.rotary_dim}")
-        exponent = torch.arange(0, spec.rotary_dim, 2, dtype=torch.float32) / spec.rotary_dim
-        self.inv_freq = (1.0 / (spec.theta ** exponent)).to(device)
+        if getattr(spec, "exact_frequencies", False):
+            exponent = torch.arange(0, spec.rotary_dim, 2, dtype=torch.float64) / spec.rotary_dim
+            self.inv_freq = (float(spec.theta) ** -exponent).to(torch.float32).to(device)
+        else:
+            exponent = torch.arange(0, spec.rotary_dim, 2, dtype=torch.float32) / spec.rotary_dim
+            self.inv_freq = (1.0 / (spec.theta ** exponent)).to(device)
         self.rotary_dim = spec.rotary_dim
 
 
