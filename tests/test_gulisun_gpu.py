@@ -95,6 +95,50 @@ def test_router_against_plain(experts, top, shared):
     assert torch.equal(routing.token_of.cpu()[slots.long()], torch.arange(37).repeat_interleave(top).int())
 
 
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 1.5e-2)])
+@pytest.mark.parametrize("m,batch,n,k,gap", [(1, 3, 40, 24, 8), (70, 4, 136, 64, 0), (33, 2, 8, 200, 16), (300, 5, 130, 72, 8)])
+def test_batched_product_against_torch(m, batch, n, k, gap, dtype, tol):
+    """Pieces side by side in the rows of x and of out, with and without the tensor-core form's alignment."""
+    from tinyinfer_b200 import ops
+    gen = torch.Generator().manual_seed(m + n)
+    x = torch.randn(m, 5 + batch * (k + gap), generator=gen).to(dtype)
+    w = (torch.randn(batch, n, k, generator=gen) / k ** 0.5).to(dtype)
+    bias = torch.randn(batch, n, generator=gen)
+    for offset in (0, 5 if gap != 8 else 8):
+        out = torch.full((m, 3 + batch * (n + 2)), 7.0)
+        got = ops.batched_linear(x.cuda(), w.cuda(), x_offset=offset, x_batch_stride=k + gap, k=k, out=out.cuda(),
+                                 out_offset=3, out_batch_stride=n + 2, bias=bias.cuda(), sigmoid=True).cpu()
+        for b in range(batch):
+            piece = x[:, offset + b * (k + gap):offset + b * (k + gap) + k].double()
+            want = torch.sigmoid(piece @ w[b].double().T + bias[b].double())
+            assert (got[:, 3 + b * (n + 2):3 + b * (n + 2) + n].double() - want).abs().max() <= tol
+        assert (got[:, :3] == 7.0).all() and (got[:, 3 + n:3 + n + 2] == 7.0).all()      # nothing written between the pieces
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
+@pytest.mark.parametrize("tokens,experts,top,ff,width", [(1, 4, 2, 24, 40), (150, 6, 3, 136, 64), (77, 9, 1, 40, 72)])
+def test_grouped_expert_products_against_torch(tokens, experts, top, ff, width, dtype, tol):
+    from tinyinfer_b200 import ops
+    gen = torch.Generator().manual_seed(tokens)
+    x = torch.randn(tokens, width, generator=gen)
+    router = torch.randn(experts, width, generator=gen)
+    up = (torch.randn(experts, ff, width, generator=gen) / width ** 0.5).to(dtype)
+    down = (torch.randn(experts, width, ff, generator=gen) / ff ** 0.5).to(dtype)
+    xc = x.to(dtype)
+    routing = ops.route_experts(x.cuda(), router.cuda(), top, 1e-20)
+    hidden = ops.expert_linear(xc.cuda(), up.cuda(), routing, up=True)
+    out = ops.expert_linear(hidden, down.cuda(), routing, up=False).cpu()
+    chosen, slot_of = routing.chosen.cpu().long(), routing.slot_of.cpu().long()
+    for t in range(tokens):
+        for c in range(top):
+            e = int(chosen[t, c])
+            h = torch.relu(xc[t].double() @ up[e].double().T) ** 2
+            if dtype == torch.bfloat16:
+                h = h.to(dtype).double()
+            want = h @ down[e].double().T
+            assert (out[slot_of[t, c]].double() - want).abs().max() <= tol * max(1.0, float(want.abs().max())), (t, c)
+
+
 # ------------------------------------------------------------------ whole models, every cut
 def traces_for(requests, max_live=4):
     return {"whole": helpers.trace_whole(requests), "tail": helpers.trace_decode_tail(requests, tail=32),

@@ -12,6 +12,7 @@
 // A token's result depends on its own row alone: no capacity, nothing dropped, whatever else is in the batch.
 // Nothing here reads back to the host: grids are sized for the worst case and tiles beyond the plan's count return.
 #include "common.cuh"
+#include "mma_tile.cuh"
 
 constexpr int EX_MAX_TOP = 16;
 
@@ -221,6 +222,36 @@ __global__ void __launch_bounds__(EG_THREADS) moe_gemm_kernel(
     }
 }
 
+// The same tiles on the tensor cores (bfloat16, K a multiple of 8): 32 rows x 128 columns a block, see mma_tile.cuh.
+static_assert(mt::BM == EG_BM, "the plan's row tiles serve both kernels");
+
+template <typename OutT, bool GATHER, bool RELU2>
+__global__ void __launch_bounds__(mt::THREADS) moe_gemm_mma_kernel(
+    OutT* __restrict__ out, const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+    const int* __restrict__ tiles, const int* __restrict__ num_tiles, const int* __restrict__ token_of, int N, int K) {
+    __shared__ __align__(16) __nv_bfloat16 ring[mt::SMEM_BYTES / 2];
+    __shared__ int src[mt::BM];
+    ti_grid_launch_dependents();
+    ti_grid_wait();
+    if ((int)blockIdx.y >= num_tiles[0]) return;
+    const int expert = tiles[3 * blockIdx.y], row0 = tiles[3 * blockIdx.y + 1], rows = tiles[3 * blockIdx.y + 2];
+    const int n0 = blockIdx.x * mt::BN;
+    const __nv_bfloat16* we = w + (size_t)expert * N * K;
+    if (threadIdx.x < mt::BM) src[threadIdx.x] = threadIdx.x < rows ? (GATHER ? token_of[row0 + threadIdx.x] : row0 + threadIdx.x) : -1;
+    __syncthreads();
+    float acc[2][4][4];
+    mt::tile_product(acc, ring,
+                     [&](int r) { return src[r] >= 0 ? x + (size_t)src[r] * K : nullptr; },
+                     [&](int n) { return n0 + n < N ? we + (size_t)(n0 + n) * K : nullptr; }, K, w);
+    mt::for_each_pair(acc, [&](int r, int c, float v0, float v1) {
+        if (r >= rows) return;
+        if (RELU2) { v0 = fmaxf(v0, 0.f); v0 *= v0; v1 = fmaxf(v1, 0.f); v1 *= v1; }
+        OutT* dst = out + (size_t)(row0 + r) * N + n0 + c;
+        if (n0 + c < N) dst[0] = from_f32<OutT>(v0);
+        if (n0 + c + 1 < N) dst[1] = from_f32<OutT>(v1);
+    });
+}
+
 TI_API int ti_moe_tile_rows() { return EG_BM; }
 
 // up != 0: x [tokens, K] gathered through token_of, out [slots, N] in the compute dtype after max(v, 0)^2;
@@ -234,6 +265,10 @@ TI_API int ti_moe_gemm(void* out, const void* x, const void* w, const int* tiles
     if (dtype == TI_F32) {
         if (up) ti_launch(moe_gemm_kernel<float, float, true, true>, grid, EG_THREADS, 0, stream, (float*)out, (const float*)x, (const float*)w, tiles, num_tiles, token_of, N, K);
         else ti_launch(moe_gemm_kernel<float, float, false, false>, grid, EG_THREADS, 0, stream, (float*)out, (const float*)x, (const float*)w, tiles, num_tiles, token_of, N, K);
+    } else if (dtype == TI_BF16 && K % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0) {
+        dim3 mgrid((N + mt::BN - 1) / mt::BN, max_tiles);
+        if (up) ti_launch(moe_gemm_mma_kernel<B, true, true>, mgrid, mt::THREADS, 0, stream, (B*)out, (const B*)x, (const B*)w, tiles, num_tiles, token_of, N, K);
+        else ti_launch(moe_gemm_mma_kernel<float, false, false>, mgrid, mt::THREADS, 0, stream, (float*)out, (const B*)x, (const B*)w, tiles, num_tiles, token_of, N, K);
     } else if (dtype == TI_BF16) {
         if (up) ti_launch(moe_gemm_kernel<B, B, true, true>, grid, EG_THREADS, 0, stream, (B*)out, (const B*)x, (const B*)w, tiles, num_tiles, token_of, N, K);
         else ti_launch(moe_gemm_kernel<B, float, false, false>, grid, EG_THREADS, 0, stream, (float*)out, (const B*)x, (const B*)w, tiles, num_tiles, token_of, N, K);

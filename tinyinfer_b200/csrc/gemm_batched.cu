@@ -5,6 +5,7 @@
 // float32 FMA accumulation in a fixed k order; a row's result does not depend on which other rows share its tile.
 // act: 0 none, 1 logistic sigmoid.
 #include "common.cuh"
+#include "mma_tile.cuh"
 
 constexpr int GB_BM = 64, GB_BN = 64, GB_BK = 16, GB_THREADS = 256;
 
@@ -69,6 +70,38 @@ __global__ void __launch_bounds__(GB_THREADS) gemm_batched_kernel(
     }
 }
 
+// The same product on the tensor cores (bfloat16; every stride, offset and K a multiple of 8): see mma_tile.cuh.
+template <typename OutT, int ACT>
+__global__ void __launch_bounds__(mt::THREADS) gemm_batched_mma_kernel(
+    OutT* __restrict__ out, const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+    const float* __restrict__ bias, GbShape s) {
+    __shared__ __align__(16) __nv_bfloat16 ring[mt::SMEM_BYTES / 2];
+    ti_grid_launch_dependents();
+    ti_grid_wait();
+    const int b = blockIdx.z;
+    const int m0 = blockIdx.y * mt::BM, n0 = blockIdx.x * mt::BN;
+    const __nv_bfloat16* xb = x + (size_t)b * s.sx;
+    const __nv_bfloat16* wb = w + (size_t)b * s.sw;
+    out += (size_t)b * s.so;
+    float acc[2][4][4];
+    mt::tile_product(acc, ring,
+                     [&](int r) { return m0 + r < s.M ? xb + (size_t)(m0 + r) * s.ldx : nullptr; },
+                     [&](int n) { return n0 + n < s.N ? wb + (size_t)(n0 + n) * s.ldw : nullptr; }, s.K, w);
+    mt::for_each_pair(acc, [&](int r, int c, float v0, float v1) {
+        const int m = m0 + r, n = n0 + c;
+        if (m >= s.M) return;
+        float v[2] = {v0, v1};
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            if (n + e >= s.N) continue;
+            float u = v[e];
+            if (bias) u += bias[(size_t)b * s.sbias + n + e];
+            if (ACT == 1) u = 1.f / (1.f + expf(-u));
+            out[(size_t)m * s.ldo + n + e] = from_f32<OutT>(u);
+        }
+    });
+}
+
 TI_API int ti_gemm_batched(void* out, const void* x, const void* w, const float* bias, int batch, int M, int N, int K,
                            long long ldx, long long sx, long long ldw, long long sw, long long ldo, long long so,
                            long long sbias, int act, int out_f32, int dtype, cudaStream_t stream) {
@@ -83,6 +116,14 @@ TI_API int ti_gemm_batched(void* out, const void* x, const void* w, const float*
 #define GB_LAUNCH(T, O, A) ti_launch(gemm_batched_kernel<T, O, A>, grid, GB_THREADS, 0, stream, (O*)out, (const T*)x, (const T*)w, bias, s)
     if (dtype == TI_F32) {
         if (act) GB_LAUNCH(float, float, 1); else GB_LAUNCH(float, float, 0);
+    } else if (dtype == TI_BF16 && K % 8 == 0 && ldx % 8 == 0 && sx % 8 == 0 && ldw % 8 == 0 && sw % 8 == 0 &&
+               ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0) {
+        dim3 mgrid((N + mt::BN - 1) / mt::BN, (M + mt::BM - 1) / mt::BM, batch);
+        TI_REQUIRE(mgrid.y <= 65535, "gemm_batched: too many rows");
+#define GB_MMA(O, A) ti_launch(gemm_batched_mma_kernel<O, A>, mgrid, mt::THREADS, 0, stream, (O*)out, (const B*)x, (const B*)w, bias, s)
+        if (out_f32) { if (act) GB_MMA(float, 1); else GB_MMA(float, 0); }
+        else { if (act) GB_MMA(B, 1); else GB_MMA(B, 0); }
+#undef GB_MMA
     } else if (dtype == TI_BF16) {
         if (out_f32) { if (act) GB_LAUNCH(B, float, 1); else GB_LAUNCH(B, float, 0); }
         else { if (act) GB_LAUNCH(B, B, 1); else GB_LAUNCH(B, B, 0); }

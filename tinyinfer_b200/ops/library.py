@@ -35,7 +35,7 @@ LIBRARIES: Dict[str, dict] = {
     "core": dict(sources=["runtime.cu", "elementwise.cu", "rope_append.cu",
                           "attention_generic.cu", "gemm_simt.cu", "sampling.cu", "stream.cu",
                           "gemm_batched.cu", "latent_attention.cu", "recurrent.cu", "experts.cu"],
-                 headers=["common.cuh"], link=[]),
+                 headers=["common.cuh", "mma_tile.cuh"], link=[]),
     # bfloat16 tensor-core kernels (tcgen05 + TMA); only a bfloat16 model loads it
     "sm100": dict(sources=["runtime.cu", "sm100_host.cu", "gemm_tcgen05.cu", "attention_mma.cu",
                            "attention_prefill_tcgen05.cu", "attention_prefill_pair_tcgen05.cu", "gemm_pair_tcgen05.cu"],
