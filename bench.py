@@ -18,6 +18,10 @@ of 512 beside decoded tokens) and ``cpu_baseline_s`` (the tiny configurations th
 CPU implementation of the tests, in seconds, beside the engine's time for the same requests).
 ``--skip-extras`` leaves them out.
 
+``--design gulisun`` leaves the headline workload alone and instead prints one JSON line with the prefill and
+decode throughput of the Gulisun design (latent attention, gated recurrences, routed experts) at two sizes with
+the layer sizes of real models, each beside the Qwen3 preset of the same width and number of layers.
+
 ``--impl reference`` runs the unmodified reference project from ``baseline/_ref`` through its own
 public API (``tinyinfer.LLM(Config(...))``, ``add_request``, ``step``) on a model folder of the same
 shape written with random weights, at the same batch, context, steps and warm-up, and prints the
@@ -505,6 +509,120 @@ def reference_arm(args) -> int:
     return 0
 
 
+# ---------------------------------------------------------------------------------- another design beside Qwen3
+def gulisun_numbers(cfg, batch, context):
+    """Per token: matrix elements a token multiplies (active experts only) and attention flops per key; per decode
+    step: bytes that must be read (dense weights, the experts a batch of this size is expected to touch, the cached
+    rows of every latent-attention layer, the head)."""
+    w, macs, dense, expert_bytes, attn_per_key, cache_per_token = cfg.width, 0, 0, 0.0, 0.0, 0
+    for layer in cfg.layers:
+        m, f = layer["mixer"], layer.get("mlp")
+        if layer["type"].startswith("latent"):
+            h, d, r, v, qr, kr = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["q_rank"], m["kv_rank"]
+            own = 0 if "kv_from" in m else (kr + r) * w
+            part = qr * w + own + h * (d + r) * qr + h * d * kr + h * v * kr + w * h * v
+            attn_per_key += 2.0 * h * (kr + r) + 2.0 * h * kr
+            cache_per_token += (kr + r) * 2                      # every latent layer reads its rows, shared or not
+        else:
+            R, B = m["width"], m["blocks"]
+            part = 2 * R * w + 2 * R * (R // B) + w * R
+        macs += part
+        dense += part
+        if f is not None:
+            e, top, ff = f["router"]["experts"], f["router"]["top"], f["expert"]["ff"]
+            shared = f["shared"]["ff"] if f.get("shared") else 0
+            macs += top * 2 * ff * w + 2 * shared * w + e * w
+            dense += 2 * shared * w + e * w
+            touched = e * (1.0 - (1.0 - top / e) ** batch)
+            expert_bytes += touched * 2 * ff * w * 2
+    head = cfg.vocab * w
+    step_bytes = dense * 2 + expert_bytes + head * 2 + batch * context * cache_per_token
+    return dict(macs=macs, attn_per_key=attn_per_key, head=head, step_bytes=step_bytes)
+
+
+def measure_design(cfg, peaks, flops_of_prefill, bytes_of_step, batch, context, steps, warmup, prefill_tokens):
+    """Prefill of one prompt and decode at ``batch`` requests of ``context`` tokens, device-timed, through the
+    step function (the same measurement as the headline's)."""
+    import torch
+    from tinyinfer_b200 import EngineConfig, ops
+    from tinyinfer_b200.engine.batch import StepEntry
+    from tinyinfer_b200.engine.llm import LLM
+    page = 64
+    pages = (context + page - 1) // page * batch + (prefill_tokens + page - 1) // page + 8
+    llm = LLM(cfg, EngineConfig(max_num_batched_tokens=max(prefill_tokens, batch), max_num_seqs=batch, max_model_len=context,
+                                kvcache_block_size=page, num_kvcache_blocks=pages, dtype="bfloat16",
+                                max_live_requests=batch + 2), random_weights=2)
+    runner = llm.runner
+    vocab = llm.model.spec.vocab_size
+    rng = random.Random(0)
+    for t in runner.storage.kv:
+        if t is not None:
+            t.normal_(0.0, 1.0)
+    prompt = [rng.randrange(vocab) for _ in range(prefill_tokens)]
+
+    def prefill_once(tag):
+        runner.step([StepEntry(tag, prompt, [len(prompt) - 1])])
+        runner.release(tag)
+    for i in range(2):
+        prefill_once(f"pw{i}")
+    prefill_ms = min(event_time(lambda i=i: prefill_once(f"p{i}")) for i in range(3))
+    total = steps + warmup
+    rids = [f"d{i}" for i in range(batch)]
+    for rid in rids:
+        fast_forward(runner, rid, context - total)
+    feeds = [[rng.randrange(vocab) for _ in range(batch)] for _ in range(total)]
+
+    def one(tokens):
+        ops.argmax(runner.step([StepEntry(rid, [tok], [0]) for rid, tok in zip(rids, tokens)]))
+    for k in range(warmup):
+        one(feeds[k])
+    launches0 = ops.launch_count()
+    ms = event_time(lambda: [one(feeds[warmup + k]) for k in range(steps)]) / steps
+    launches = (ops.launch_count() - launches0) / steps
+    runner.check_status()
+    out = {"prefill_tokens": prefill_tokens, "prefill_ms": prefill_ms, "prefill_tok_s": prefill_tokens / (prefill_ms / 1e3),
+           "prefill_frac_of_tensor_peak": flops_of_prefill / (prefill_ms / 1e3) / (peaks["bf16_tflops_sustained"] * 1e12),
+           "decode_batch": batch, "decode_context": context, "decode_ms_per_step": ms, "decode_tok_s": batch / (ms / 1e3),
+           "decode_frac_of_hbm": bytes_of_step / (ms / 1e3) / 1e9 / peaks["hbm_gbs"],
+           "decode_step_gbytes": bytes_of_step / 1e9, "kernels_per_decode_step": launches,
+           "graph_replays": runner.graph_replays, "weights_gb": llm.model.weight_bytes() / 1e9}
+    for rid in rids:
+        runner.release(rid)
+    release_engine(llm)
+    return out
+
+
+def design_comparison(args) -> int:
+    """``--design gulisun``: the design at two sizes beside the Qwen3 preset of the same width, both cut to the same
+    number of layers; one JSON line."""
+    from tinyinfer_b200.config import preset_config
+    peaks, peak_source = load_peaks()
+    steps, warmup = args.steps, max(3, args.warmup)
+    batch, context, prefill_tokens = args.batch, min(args.context, 2048), 2048
+    sizes = {}
+    for ours, theirs in (("gulisun-1b", "0.6b"), ("gulisun-2b", "1.7b")):
+        g = preset_config(ours)
+        layers = len(g.layers)
+        numbers = gulisun_numbers(g, batch, context)
+        t = prefill_tokens
+        flops = 2.0 * numbers["macs"] * t + numbers["attn_per_key"] * t * (t + 1) / 2.0 + 2.0 * numbers["head"]
+        row = {"layers": layers, "gulisun": measure_design(g, peaks, flops, numbers["step_bytes"], batch, context, steps,
+                                                           warmup, prefill_tokens)}
+        q = preset_config(theirs, num_hidden_layers=layers)
+        qn = model_numbers(q, layers)
+        row["qwen3"] = measure_design(q, peaks, prefill_flops(q, layers, t, 1),
+                                      qn["weight_bytes"] + batch * context * qn["kv_bytes_per_token"], batch, context,
+                                      steps, warmup, prefill_tokens)
+        row["qwen3"]["preset"] = theirs
+        row["prefill_ratio"] = row["gulisun"]["prefill_tok_s"] / row["qwen3"]["prefill_tok_s"]
+        row["decode_ratio"] = row["gulisun"]["decode_tok_s"] / row["qwen3"]["decode_tok_s"]
+        sizes[ours] = row
+    print(json.dumps({"metric": "prefill and decode tok/s of the Gulisun design beside Qwen3 at equal width and depth",
+                      "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "bf16",
+                      "data": "synthetic token ids, random-init weights", "peaks": peak_source, "sizes": sizes}))
+    return 0
+
+
 # ---------------------------------------------------------------------------------- this engine
 def main() -> int:
     ap = argparse.ArgumentParser()
@@ -520,6 +638,8 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch")
     ap.add_argument("--skip-extras", action="store_true", help="leave out the 'configs' of the line")
     ap.add_argument("--extras", default="32b,mix,cpu", help="which of the other configurations to run")
+    ap.add_argument("--design", default="", choices=["", "gulisun"],
+                    help="instead of the headline: prefill and decode of this design beside Qwen3 at equal size")
     ap.add_argument("--ref-block-size", type=int, default=256, help="reference arm: its kvcache_block_size (its default)")
     ap.add_argument("--ref-step-tokens", type=int, default=32,
                     help="reference arm: its max_num_batched_tokens (more than 32 tokens in a step crash its binding here)")
@@ -534,6 +654,8 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.design:
+        return design_comparison(args)
 
     import torch
     from tinyinfer_b200 import EngineConfig, SamplingParams

@@ -214,6 +214,14 @@ def test_far_keys_carry_the_score(tmp_path):
                   helpers.trace_chunked(requests, seed=7)):
         got, _ = run(folder, "float32", steps, page=16)
         assert helpers.first_bad(got, want, TOL["float32"]) is None
+    # the same through the bfloat16 kernels (rows of 48 features: the tensor-core forms for portions and for decoding)
+    folder16 = gh.write_folder(tmp_path / "m16", cfg, seed=21, dtype="bfloat16")
+    want16 = gh.plain_logits(folder16, requests)
+    for steps in (helpers.trace_whole(requests), helpers.trace_decode_tail(requests, tail=140),
+                  helpers.trace_chunked(requests, seed=7)):
+        got, _ = run(folder16, "bfloat16", steps, page=16)
+        err = row_errors(got, want16)
+        assert np.isfinite(err).all() and np.median(err) <= 2e-2 and (err > 0.15).mean() <= 0.02, np.sort(err)[-5:]
 
 
 # ------------------------------------------------------------------ long decoding through graphs

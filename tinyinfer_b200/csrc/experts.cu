@@ -17,32 +17,54 @@
 constexpr int EX_MAX_TOP = 16;
 
 // ------------------------------------------------------------------ route
-// One warp per token. Scores of up to 32 * EX_PER_LANE experts are held a lane apiece.
+// One block per token: its warps share out the experts' logits (16-byte loads of the router's rows where they are
+// aligned), then the first warp holds the scores of up to 32 * EX_PER_LANE experts, a lane apiece, and chooses.
 constexpr int EX_PER_LANE = 8;
+constexpr int EX_ROUTE_THREADS = 512;
 
 template <typename T>
-__global__ void __launch_bounds__(128) moe_route_kernel(
+__global__ void __launch_bounds__(EX_ROUTE_THREADS) moe_route_kernel(
     int* __restrict__ chosen, float* __restrict__ weight, int* __restrict__ rank, int* __restrict__ counts,
     const float* __restrict__ x32, const T* __restrict__ w_router, int num_tokens, int hidden, int experts, int top,
     float weight_eps) {
+    __shared__ float logits[32 * EX_PER_LANE];
     ti_grid_launch_dependents();
     ti_grid_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * 4 + warp;
-    if (t >= num_tokens) return;
+    const int t = blockIdx.x;
     const float* x = x32 + (size_t)t * hidden;
-    float z[EX_PER_LANE];                              // lane holds experts lane, lane + 32, ...
-#pragma unroll
-    for (int k = 0; k < EX_PER_LANE; ++k) z[k] = -INFINITY;
-    for (int e = 0; e < experts; ++e) {
+    constexpr int VEC = 16 / sizeof(T);
+    const bool aligned = hidden % VEC == 0 && ((uintptr_t)w_router & 15) == 0 && ((uintptr_t)x32 & 15) == 0;
+    for (int e = warp; e < experts; e += EX_ROUTE_THREADS / 32) {
         const T* w = w_router + (size_t)e * hidden;
         float dot = 0.f;
-        for (int i = lane; i < hidden; i += 32) dot = fmaf(x[i], to_f32(w[i]), dot);
-        dot = warp_sum(dot);
+        if (aligned) {
+            const uint4* w4 = reinterpret_cast<const uint4*>(w);
+#pragma unroll 4
+            for (int v = lane; v < hidden / VEC; v += 32) {
+                const uint4 q = w4[v];
+                const T* we = reinterpret_cast<const T*>(&q);
+                const float4* xp = reinterpret_cast<const float4*>(x + (size_t)v * VEC);
 #pragma unroll
-        for (int k = 0; k < EX_PER_LANE; ++k)
-            if ((e >> 5) == k && (e & 31) == lane) z[k] = dot;
+                for (int i = 0; i < VEC / 4; ++i) {
+                    const float4 f = xp[i];
+                    dot = fmaf(f.x, to_f32(we[4 * i]), dot);
+                    dot = fmaf(f.y, to_f32(we[4 * i + 1]), dot);
+                    dot = fmaf(f.z, to_f32(we[4 * i + 2]), dot);
+                    dot = fmaf(f.w, to_f32(we[4 * i + 3]), dot);
+                }
+            }
+        } else {
+            for (int i = lane; i < hidden; i += 32) dot = fmaf(x[i], to_f32(w[i]), dot);
+        }
+        dot = warp_sum(dot);
+        if (lane == 0) logits[e] = dot;
     }
+    __syncthreads();
+    if (warp != 0) return;
+    float z[EX_PER_LANE];                              // lane holds experts lane, lane + 32, ...
+#pragma unroll
+    for (int k = 0; k < EX_PER_LANE; ++k) z[k] = (k * 32 + lane < experts) ? logits[k * 32 + lane] : -INFINITY;
     float mx = -INFINITY;
 #pragma unroll
     for (int k = 0; k < EX_PER_LANE; ++k) mx = fmaxf(mx, z[k]);
@@ -135,12 +157,12 @@ TI_API int ti_moe_route(int* chosen, float* weight, int* rank, int* counts, int*
     if (num_tokens == 0) return 0;
     cudaError_t e = cudaMemsetAsync(counts, 0, sizeof(int) * experts, stream);
     TI_REQUIRE(e == cudaSuccess, "moe_route: %s", cudaGetErrorString(e));
-    const int blocks = (num_tokens + 3) / 4;
+    const int blocks = num_tokens;
     if (dtype == TI_F32)
-        ti_launch(moe_route_kernel<float>, blocks, 128, 0, stream, chosen, weight, rank, counts, x32, (const float*)w_router,
+        ti_launch(moe_route_kernel<float>, blocks, EX_ROUTE_THREADS, 0, stream, chosen, weight, rank, counts, x32, (const float*)w_router,
                   num_tokens, hidden, experts, top, weight_eps);
     else if (dtype == TI_BF16)
-        ti_launch(moe_route_kernel<__nv_bfloat16>, blocks, 128, 0, stream, chosen, weight, rank, counts, x32,
+        ti_launch(moe_route_kernel<__nv_bfloat16>, blocks, EX_ROUTE_THREADS, 0, stream, chosen, weight, rank, counts, x32,
                   (const __nv_bfloat16*)w_router, num_tokens, hidden, experts, top, weight_eps);
     else TI_REQUIRE(false, "moe_route: unknown dtype %d", dtype);
     TI_CHECK_LAUNCH("moe_route");

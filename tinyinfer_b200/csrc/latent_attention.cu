@@ -288,6 +288,21 @@ __global__ void latent_merge_kernel(T* __restrict__ out, const float* __restrict
     }
 }
 
+// Folds `splits` parts per (token, head) (as the attention kernels leave them) into out [T, heads, rank].
+TI_API int ti_latent_merge(void* out, const float* parts, const float* sink, int num_tokens, int heads, int rank, int splits,
+                           int dtype, cudaStream_t stream) {
+    TI_REQUIRE(num_tokens >= 0 && heads > 0 && rank > 0 && splits >= 1 && num_tokens <= 65535, "latent_merge: bad sizes");
+    if (num_tokens == 0) return 0;
+    dim3 mgrid(heads, num_tokens);
+    if (dtype == TI_F32)
+        ti_launch(latent_merge_kernel<float>, mgrid, 128, 0, stream, (float*)out, parts, sink, heads, rank, splits);
+    else if (dtype == TI_BF16)
+        ti_launch(latent_merge_kernel<__nv_bfloat16>, mgrid, 128, 0, stream, (__nv_bfloat16*)out, parts, sink, heads, rank, splits);
+    else TI_REQUIRE(false, "latent_merge: unknown dtype %d", dtype);
+    TI_CHECK_LAUNCH("latent_merge");
+    return 0;
+}
+
 template <typename T, int NV>
 static cudaError_t la_launch(dim3 grid, size_t smem, cudaStream_t stream, void* out, float* parts, const float* q,
                              const void* cache, const float* sink, const int* positions, const int* token_seq,

@@ -43,8 +43,9 @@ def _layers(pattern: str, latent: dict, recurrent: dict, mlp: dict):
     return out
 
 
-# Sizes worth running with random weights (config.json keys): a toy, and one with the layer sizes of a model of a
-# few billion parameters (width 2048, 16 heads over a latent of 512 + 64, 64 experts of 1408 of which 6 run).
+# Sizes worth running with random weights (config.json keys): a toy, and two with the layer sizes of models of one and
+# of a few billion parameters (the larger: width 2048, 16 heads over a latent of 512 + 64, 64 experts of 1408 of which 6 run),
+# eight layers each: a benchmark runs as many layers as it lists.
 PRESETS = {
     "gulisun-tiny": dict(
         vocab=256, width=64, embedding=dict(scale=8.0), norm=dict(eps=1e-5),
@@ -53,6 +54,13 @@ PRESETS = {
                             rot=dict(base=10000.0, dims=8)),
                        dict(width=64, blocks=2, conv=4),
                        dict(kind="moe", router=dict(experts=4, top=2), expert=dict(ff=32), shared=dict(ff=48)))),
+    "gulisun-1b": dict(
+        vocab=102400, width=1024, embedding=dict(scale=1.0), norm=dict(eps=1e-6),
+        layers=_layers("srkp" * 2,
+                       dict(heads=8, dim=64, rot_dim=32, vdim=64, q_rank=768, kv_rank=256, scale=96 ** -0.5,
+                            rot=dict(base=10000.0, dims=32)),
+                       dict(width=1280, blocks=5, conv=4),
+                       dict(kind="moe", router=dict(experts=32, top=4), expert=dict(ff=704), shared=dict(ff=1408)))),
     "gulisun-2b": dict(
         vocab=102400, width=2048, embedding=dict(scale=1.0), norm=dict(eps=1e-6),
         layers=_layers("srkp" * 2,

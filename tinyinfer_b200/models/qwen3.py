@@ -18,6 +18,9 @@ PRESETS = {
     "tiny": dict(vocab_size=256, hidden_size=64, num_hidden_layers=2, num_attention_heads=4,
                  num_key_value_heads=2, head_dim=16, intermediate_size=128, rms_norm_eps=1e-6,
                  rope_theta=10000.0, tie_word_embeddings=True, max_position_embeddings=512),
+    "0.6b": dict(vocab_size=151936, hidden_size=1024, num_hidden_layers=28, num_attention_heads=16,
+                 num_key_value_heads=8, head_dim=128, intermediate_size=3072, rms_norm_eps=1e-6,
+                 rope_theta=1000000.0, tie_word_embeddings=True, max_position_embeddings=40960),
     "1.7b": dict(vocab_size=151936, hidden_size=2048, num_hidden_layers=28, num_attention_heads=16,
                  num_key_value_heads=8, head_dim=128, intermediate_size=6144, rms_norm_eps=1e-6,
                  rope_theta=1000000.0, tie_word_embeddings=True, max_position_embeddings=40960),

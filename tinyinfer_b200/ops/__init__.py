@@ -58,6 +58,11 @@ _SIGNATURES = {
                             c_void_p, c_int, c_void_p],
         "ti_latent_attend": [c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_int, c_void_p],
+        "ti_latent_merge": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "ti_latent_attend_mma_ok": [c_int, c_int],
+        "ti_latent_attend_mma": [c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+                                 c_void_p, c_void_p],
         "ti_causal_conv": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                            c_int, c_int, c_int, c_int, c_void_p],
         "ti_gated_scan": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
@@ -803,12 +808,15 @@ LATENT_TARGET_BLOCKS = 296      # enough blocks to have two on every SM
 
 def latent_attention(q_rows: torch.Tensor, cache: torch.Tensor, *, heads: int, rank: int, rot: int, scale: float,
                      sink: Optional[torch.Tensor], positions: torch.Tensor, token_seq: torch.Tensor,
-                     block_table: torch.Tensor, max_context: int, window: Optional[int] = None,
+                     block_table: torch.Tensor, max_context: int, window: Optional[int] = None, step=None,
                      status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of query rows float32 [T, heads * (rank + rot)] over each token's own request's cached
     rows [c | k_rot] (``cache`` [1, pages, 1, page, rank + rot]); returns sum_j p_j c_j per head, [T, heads * rank]
     in the cache's dtype. ``sink`` float32 [heads]: exp(sink) joins every softmax denominator. ``max_context``
-    (a host number, the longest context of the step) only decides over how many blocks the keys are shared."""
+    (a host number, the longest context of the step) only decides over how many blocks the keys are shared.
+    ``step`` (the StepContext): with it a bfloat16 cache whose rows are a multiple of 8 features runs on the
+    tensor cores, prompt portions and decoded tokens in their own forms; without it, in float32 or with a window,
+    the float32-arithmetic kernel runs."""
     _check(q_rows, "q_rows", torch.float32, 2)
     _check(cache, "cache", None, 5)
     _check(positions, "positions", torch.int32, 1)
@@ -824,14 +832,36 @@ def latent_attention(q_rows: torch.Tensor, cache: torch.Tensor, *, heads: int, r
     out = torch.empty((t, heads * rank), dtype=cache.dtype, device=cache.device)
     if t == 0:
         return out
-    blocks = t * ((heads + 7) // 8)
-    splits = 1
-    if blocks < LATENT_TARGET_BLOCKS and max_context >= 2 * LATENT_SPLIT_MIN_KEYS:
-        splits = max(1, min(-(-LATENT_TARGET_BLOCKS // blocks), int(max_context) // LATENT_SPLIT_MIN_KEYS, 64))
-    parts, parts_floats = None, 0
-    if splits > 1:
+
+    def share_out(blocks: int) -> int:
+        if blocks < LATENT_TARGET_BLOCKS and max_context >= 2 * LATENT_SPLIT_MIN_KEYS:
+            return max(1, min(-(-LATENT_TARGET_BLOCKS // blocks), int(max_context) // LATENT_SPLIT_MIN_KEYS, 64))
+        return 1
+
+    def scratch(splits: int):
+        if splits == 1:
+            return None, 0
         parts = _decode_scratch(cache.device, t * heads * splits * (rank + 2))
-        parts_floats = parts.numel()
+        return parts, parts.numel()
+
+    if (step is not None and cache.dtype == torch.bfloat16 and not window
+            and int(_fn("core", "ti_latent_attend_mma_ok")(rank, rot))):
+        decode = step.max_q_len == 1
+        rows = 16 if decode else 64
+        per_block = min(heads, rows)
+        tokens_per_block = 1 if decode else max(1, rows // per_block)
+        splits = share_out(-(-t // tokens_per_block) * -(-heads // per_block))
+        parts, parts_floats = scratch(splits)
+        _run("core", "ti_latent_attend_mma", out.data_ptr(), _ptr(parts), parts_floats, q_rows.data_ptr(), cache.data_ptr(),
+             _ptr(sink), positions.data_ptr(), token_seq.data_ptr(), step.cu_seqlens.data_ptr(), block_table.data_ptr(),
+             block_table.shape[1], step.num_seqs, t, heads, rank, rot, cache.shape[3], cache.shape[1], float(scale), splits,
+             int(decode), _ptr(status), _stream())
+        if splits > 1:
+            _run("core", "ti_latent_merge", out.data_ptr(), parts.data_ptr(), _ptr(sink), t, heads, rank, splits,
+                 _dtype_code(cache), _stream())
+        return out
+    splits = share_out(t * ((heads + 7) // 8))
+    parts, parts_floats = scratch(splits)
     _run("core", "ti_latent_attend", out.data_ptr(), _ptr(parts), parts_floats, q_rows.data_ptr(), cache.data_ptr(),
          _ptr(sink), positions.data_ptr(), token_seq.data_ptr(), block_table.data_ptr(), block_table.shape[1], t, heads,
          rank, rot, cache.shape[3], cache.shape[1], float(scale), int(window or 0), splits, _ptr(status),

@@ -34,7 +34,8 @@ LIBRARIES: Dict[str, dict] = {
     # every dtype, every shape: the 32-bit path and the general bfloat16 path
     "core": dict(sources=["runtime.cu", "elementwise.cu", "rope_append.cu",
                           "attention_generic.cu", "gemm_simt.cu", "sampling.cu", "stream.cu",
-                          "gemm_batched.cu", "latent_attention.cu", "recurrent.cu", "experts.cu"],
+                          "gemm_batched.cu", "latent_attention.cu", "latent_attention_mma.cu", "recurrent.cu",
+                          "experts.cu"],
                  headers=["common.cuh", "mma_tile.cuh"], link=[]),
     # bfloat16 tensor-core kernels (tcgen05 + TMA); only a bfloat16 model loads it
     "sm100": dict(sources=["runtime.cu", "sm100_host.cu", "gemm_tcgen05.cu", "attention_mma.cu",

@@ -86,7 +86,7 @@ class LatentAttention(Mixer):
         mixed = ops.latent_attention(
             rows, cache.kv, heads=s.num_heads, rank=s.kv_rank, rot=s.rot_dim, scale=s.scale, sink=self.sink,
             positions=step.positions, token_seq=step.token_seq, block_table=cache.block_table,
-            max_context=step.max_context, window=s.window, status=step.status)
+            max_context=step.max_context, window=s.window, step=step, status=step.status)
         values = ops.batched_linear(mixed, self.w_uv, x_batch_stride=s.kv_rank, k=s.kv_rank)    # [T, H * v_dim]
         return ops.linear(values, self.w_o)
 
