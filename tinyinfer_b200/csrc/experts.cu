@@ -247,25 +247,26 @@ __global__ void __launch_bounds__(EG_THREADS) moe_gemm_kernel(
 // The same tiles on the tensor cores (bfloat16, K a multiple of 8): 32 rows x 128 columns a block, see mma_tile.cuh.
 static_assert(mt::BM == EG_BM, "the plan's row tiles serve both kernels");
 
-template <typename OutT, bool GATHER, bool RELU2>
+// MI = 2: row tiles of 32; MI = 4: of 64 (steps that bring an expert many rows: half the trips of its weights).
+template <typename OutT, bool GATHER, bool RELU2, int MI>
 __global__ void __launch_bounds__(mt::THREADS) moe_gemm_mma_kernel(
     OutT* __restrict__ out, const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
     const int* __restrict__ tiles, const int* __restrict__ num_tiles, const int* __restrict__ token_of, int N, int K) {
-    __shared__ __align__(16) __nv_bfloat16 ring[mt::SMEM_BYTES / 2];
-    __shared__ int src[mt::BM];
+    __shared__ __align__(16) __nv_bfloat16 ring[mt::Ring<MI>::BYTES / 2];
+    __shared__ int src[16 * MI];
     ti_grid_launch_dependents();
     ti_grid_wait();
     if ((int)blockIdx.y >= num_tiles[0]) return;
     const int expert = tiles[3 * blockIdx.y], row0 = tiles[3 * blockIdx.y + 1], rows = tiles[3 * blockIdx.y + 2];
     const int n0 = blockIdx.x * mt::BN;
     const __nv_bfloat16* we = w + (size_t)expert * N * K;
-    if (threadIdx.x < mt::BM) src[threadIdx.x] = threadIdx.x < rows ? (GATHER ? token_of[row0 + threadIdx.x] : row0 + threadIdx.x) : -1;
+    if (threadIdx.x < 16 * MI) src[threadIdx.x] = threadIdx.x < rows ? (GATHER ? token_of[row0 + threadIdx.x] : row0 + threadIdx.x) : -1;
     __syncthreads();
-    float acc[2][4][4];
-    mt::tile_product(acc, ring,
+    float acc[MI][4][4];
+    mt::tile_product<MI>(acc, ring,
                      [&](int r) { return src[r] >= 0 ? x + (size_t)src[r] * K : nullptr; },
                      [&](int n) { return n0 + n < N ? we + (size_t)(n0 + n) * K : nullptr; }, K, w);
-    mt::for_each_pair(acc, [&](int r, int c, float v0, float v1) {
+    mt::for_each_pair<MI>(acc, [&](int r, int c, float v0, float v1) {
         if (r >= rows) return;
         if (RELU2) { v0 = fmaxf(v0, 0.f); v0 *= v0; v1 = fmaxf(v1, 0.f); v1 *= v1; }
         OutT* dst = out + (size_t)(row0 + r) * N + n0 + c;
@@ -278,19 +279,26 @@ TI_API int ti_moe_tile_rows() { return EG_BM; }
 
 // up != 0: x [tokens, K] gathered through token_of, out [slots, N] in the compute dtype after max(v, 0)^2;
 // else x [slots, K], out [slots, N] float32. w [experts, N, K]. max_tiles: the grid's height.
+// 1 if row tiles of 64 are taken for these operands (the tensor-core form), else the plan must cut tiles of 32.
+TI_API int ti_moe_wide_tiles_ok(int K, int dtype) { return dtype == TI_BF16 && K % 8 == 0 ? 1 : 0; }
+
 TI_API int ti_moe_gemm(void* out, const void* x, const void* w, const int* tiles, const int* num_tiles, const int* token_of,
-                       int N, int K, int max_tiles, int up, int dtype, cudaStream_t stream) {
+                       int N, int K, int max_tiles, int tile_rows, int up, int dtype, cudaStream_t stream) {
     TI_REQUIRE(N > 0 && K > 0 && max_tiles >= 0 && max_tiles <= 65535, "moe_gemm: bad sizes");
+    const bool tensor_cores = dtype == TI_BF16 && K % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0;
+    TI_REQUIRE(tile_rows == EG_BM || (tile_rows == 64 && tensor_cores), "moe_gemm: row tiles of %d are not taken here", tile_rows);
     if (max_tiles == 0) return 0;
     dim3 grid((N + EG_BN - 1) / EG_BN, max_tiles);
     typedef __nv_bfloat16 B;
     if (dtype == TI_F32) {
         if (up) ti_launch(moe_gemm_kernel<float, float, true, true>, grid, EG_THREADS, 0, stream, (float*)out, (const float*)x, (const float*)w, tiles, num_tiles, token_of, N, K);
         else ti_launch(moe_gemm_kernel<float, float, false, false>, grid, EG_THREADS, 0, stream, (float*)out, (const float*)x, (const float*)w, tiles, num_tiles, token_of, N, K);
-    } else if (dtype == TI_BF16 && K % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0) {
+    } else if (tensor_cores) {
         dim3 mgrid((N + mt::BN - 1) / mt::BN, max_tiles);
-        if (up) ti_launch(moe_gemm_mma_kernel<B, true, true>, mgrid, mt::THREADS, 0, stream, (B*)out, (const B*)x, (const B*)w, tiles, num_tiles, token_of, N, K);
-        else ti_launch(moe_gemm_mma_kernel<float, false, false>, mgrid, mt::THREADS, 0, stream, (float*)out, (const B*)x, (const B*)w, tiles, num_tiles, token_of, N, K);
+#define EG_MMA(O, G, R, MI) ti_launch(moe_gemm_mma_kernel<O, G, R, MI>, mgrid, mt::THREADS, 0, stream, (O*)out, (const B*)x, (const B*)w, tiles, num_tiles, token_of, N, K)
+        if (tile_rows == 64) { if (up) EG_MMA(B, true, true, 4); else EG_MMA(float, false, false, 4); }
+        else { if (up) EG_MMA(B, true, true, 2); else EG_MMA(float, false, false, 2); }
+#undef EG_MMA
     } else if (dtype == TI_BF16) {
         if (up) ti_launch(moe_gemm_kernel<B, B, true, true>, grid, EG_THREADS, 0, stream, (B*)out, (const B*)x, (const B*)w, tiles, num_tiles, token_of, N, K);
         else ti_launch(moe_gemm_kernel<B, float, false, false>, grid, EG_THREADS, 0, stream, (float*)out, (const B*)x, (const B*)w, tiles, num_tiles, token_of, N, K);

@@ -84,10 +84,10 @@ __global__ void __launch_bounds__(mt::THREADS) gemm_batched_mma_kernel(
     const __nv_bfloat16* wb = w + (size_t)b * s.sw;
     out += (size_t)b * s.so;
     float acc[2][4][4];
-    mt::tile_product(acc, ring,
+    mt::tile_product<2>(acc, ring,
                      [&](int r) { return m0 + r < s.M ? xb + (size_t)(m0 + r) * s.ldx : nullptr; },
                      [&](int n) { return n0 + n < s.N ? wb + (size_t)(n0 + n) * s.ldw : nullptr; }, s.K, w);
-    mt::for_each_pair(acc, [&](int r, int c, float v0, float v1) {
+    mt::for_each_pair<2>(acc, [&](int r, int c, float v0, float v1) {
         const int m = m0 + r, n = n0 + c;
         if (m >= s.M) return;
         float v[2] = {v0, v1};

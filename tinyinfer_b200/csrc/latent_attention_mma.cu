@@ -120,24 +120,29 @@ __global__ void __launch_bounds__(128 * MW, 1) latent_attend_mma_kernel(Args a) 
     const int* table = a.block_table + (size_t)seq * a.max_blocks;
     const int chunks = dkp / 8;                                // 16-byte pieces of a row in shared memory
     const int real_chunks = dk / 8;
+    // a warp fetches whole rows: the row's page is looked up once, its 16-byte pieces go a lane apiece
     auto load_tile = [&](int j0, int buf) {
         __nv_bfloat16* dst = Ks + buf * KEYS * lds;
-        for (int i = tid; i < KEYS * chunks; i += THREADS) {
-            const int j = i / chunks, c = i % chunks;
-            const int key = j0 + j;
-            const __nv_bfloat16* src = a.cache;
-            bool ok = key < last_key && c < real_chunks;
-            if (ok) {
+        constexpr int PER_WARP = KEYS / (4 * MW);
+        const __nv_bfloat16* src[PER_WARP];
+#pragma unroll
+        for (int i = 0; i < PER_WARP; ++i) {
+            const int key = j0 + warp * PER_WARP + i;
+            src[i] = nullptr;
+            if (key < last_key) {
                 const int logical = key / a.page_size;
                 const int page = logical < a.max_blocks ? table[logical] : -1;
-                if (page >= 0 && page < a.num_pages) {
-                    src = a.cache + ((size_t)page * a.page_size + key % a.page_size) * dk + c * 8;
-                } else {
-                    ok = false;
-                    if (a.status) atomicExch(a.status, 2);     // a visible key without a page
-                }
+                if (page >= 0 && page < a.num_pages) src[i] = a.cache + ((size_t)page * a.page_size + key % a.page_size) * dk;
+                else if (lane == 0 && a.status) atomicExch(a.status, 2);      // a visible key without a page
             }
-            mt::cp16(dst + j * lds + c * 8, src, ok);
+        }
+#pragma unroll
+        for (int i = 0; i < PER_WARP; ++i) {
+            __nv_bfloat16* row = dst + (warp * PER_WARP + i) * lds;
+            for (int c = lane; c < chunks; c += 32) {
+                const bool ok = src[i] != nullptr && c < real_chunks;
+                mt::cp16(row + c * 8, ok ? src[i] + c * 8 : a.cache, ok);
+            }
         }
     };
     float o[NT][4];

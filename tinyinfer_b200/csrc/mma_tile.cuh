@@ -1,8 +1,8 @@
-// A 32 x 128 output tile of x . w^T on the warp-level tensor-core path (mma.sync m16n8k16, bfloat16 in, float32
+// A 32 x 128 (MI = 2) or 64 x 128 (MI = 4) output tile of x . w^T on the warp-level tensor-core path (mma.sync m16n8k16, bfloat16 in, float32
 // accumulators) for products whose row tiles are too short, too scattered or too many-shaped for the tcgen05
 // kernels' 128-row tiles and tensor maps: the row tiles of routed experts (often a handful of rows an expert), the
 // per-head and per-block products of the batched form. Four warps; warp w owns columns [32 w, 32 w + 32) of the
-// tile for all 32 rows. Operands come through a ring of three stages filled with 16-byte cp.async copies (rows
+// tile for all rows. Operands come through a ring of three stages filled with 16-byte cp.async copies (rows
 // and k beyond the operands are zero-filled), so a block streams its 128 weight rows at full width whatever the
 // number of valid x rows. A row's result does not depend on the other rows of its tile, and k is walked in order.
 //
@@ -15,8 +15,9 @@
 namespace mt {
 constexpr int BM = 32, BN = 128, BK = 32, STAGES = 3, THREADS = 128;
 constexpr int LDS = BK + 8;                                   // halves per row in shared memory: ldmatrix without conflicts
-constexpr int A_HALVES = BM * LDS, B_HALVES = BN * LDS;
-constexpr int SMEM_BYTES = STAGES * (A_HALVES + B_HALVES) * 2;
+constexpr int B_HALVES = BN * LDS;
+template <int MI> struct Ring { static constexpr int BYTES = STAGES * (16 * MI * LDS + B_HALVES) * 2; };
+constexpr int SMEM_BYTES = Ring<2>::BYTES;
 
 __device__ __forceinline__ void cp16(void* dst, const void* src, bool valid) {
     const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
@@ -38,28 +39,34 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const unsigned (&a)[4], 
 }
 
 // acc[mi][ni][4]: rows 16 mi + (lane / 4) (+ 8 for elements 2, 3), columns 32 warp + 8 ni + 2 (lane % 4) (+ 1).
-template <typename ARow, typename BRow>
-__device__ __forceinline__ void tile_product(float (&acc)[2][4][4], __nv_bfloat16* smem, ARow a_row, BRow b_row, int K,
+template <int MI, typename ARow, typename BRow>
+__device__ __forceinline__ void tile_product(float (&acc)[MI][4][4], __nv_bfloat16* smem, ARow a_row, BRow b_row, int K,
                                              const __nv_bfloat16* safe) {
+    constexpr int A_HALVES = 16 * MI * LDS;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     __nv_bfloat16* As = smem;
     __nv_bfloat16* Bs = smem + STAGES * A_HALVES;
 #pragma unroll
-    for (int mi = 0; mi < 2; ++mi)
+    for (int mi = 0; mi < MI; ++mi)
 #pragma unroll
         for (int ni = 0; ni < 4; ++ni)
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[mi][ni][e] = 0.f;
-    // what this thread copies in every stage: one 16-byte piece of x, four of w
+    // what this thread copies in every stage: MI / 2 16-byte pieces of x, four of w
     const int a_r = tid >> 2, a_c = (tid & 3) * 8;
-    const __nv_bfloat16* a_src = a_row(a_r);
+    const __nv_bfloat16* a_src[MI / 2];
+#pragma unroll
+    for (int i = 0; i < MI / 2; ++i) a_src[i] = a_row(a_r + 32 * i);
     const __nv_bfloat16* b_src[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) b_src[i] = b_row((tid >> 2) + 32 * i);
     const int steps = (K + BK - 1) / BK;
     auto load = [&](int step, int stage) {
         const int k = step * BK + a_c;
-        cp16(As + stage * A_HALVES + a_r * LDS + a_c, (a_src && k < K) ? a_src + k : safe, a_src != nullptr && k < K);
+#pragma unroll
+        for (int i = 0; i < MI / 2; ++i)
+            cp16(As + stage * A_HALVES + (a_r + 32 * i) * LDS + a_c, (a_src[i] && k < K) ? a_src[i] + k : safe,
+                 a_src[i] != nullptr && k < K);
 #pragma unroll
         for (int i = 0; i < 4; ++i)
             cp16(Bs + stage * B_HALVES + ((tid >> 2) + 32 * i) * LDS + a_c, (b_src[i] && k < K) ? b_src[i] + k : safe,
@@ -79,15 +86,15 @@ __device__ __forceinline__ void tile_product(float (&acc)[2][4][4], __nv_bfloat1
         const __nv_bfloat16* b = Bs + (step % STAGES) * B_HALVES + warp * 32 * LDS;
 #pragma unroll
         for (int kk = 0; kk < BK; kk += 16) {
-            unsigned af[2][4], bf[2][4];
+            unsigned af[MI][4], bf[2][4];
 #pragma unroll
-            for (int mi = 0; mi < 2; ++mi)      // 16 x 16 of x: matrices (rows 0-7, k 0-7), (rows 8-15, k 0-7), (rows 0-7, k 8-15), (rows 8-15, k 8-15)
+            for (int mi = 0; mi < MI; ++mi)     // 16 x 16 of x: matrices (rows 0-7, k 0-7), (rows 8-15, k 0-7), (rows 0-7, k 8-15), (rows 8-15, k 8-15)
                 ldmatrix_x4(af[mi], a + (mi * 16 + (lane & 15)) * LDS + kk + (lane >> 4) * 8);
 #pragma unroll
             for (int nj = 0; nj < 2; ++nj)      // 16 columns x 16 of k: (n 0-7, k 0-7), (n 0-7, k 8-15), (n 8-15, k 0-7), (n 8-15, k 8-15)
                 ldmatrix_x4(bf[nj], b + (nj * 16 + (lane & 7) + ((lane >> 4) << 3)) * LDS + kk + ((lane >> 3) & 1) * 8);
 #pragma unroll
-            for (int mi = 0; mi < 2; ++mi)
+            for (int mi = 0; mi < MI; ++mi)
 #pragma unroll
                 for (int ni = 0; ni < 4; ++ni)
                     mma16816(acc[mi][ni], af[mi], bf[ni >> 1][(ni & 1) * 2], bf[ni >> 1][(ni & 1) * 2 + 1]);
@@ -98,11 +105,11 @@ __device__ __forceinline__ void tile_product(float (&acc)[2][4][4], __nv_bfloat1
 }
 
 // Calls f(row, col, value) for the two neighbouring columns (col, col + 1) a thread holds: f(row, col, v0, v1).
-template <typename F>
-__device__ __forceinline__ void for_each_pair(const float (&acc)[2][4][4], F f) {
+template <int MI, typename F>
+__device__ __forceinline__ void for_each_pair(const float (&acc)[MI][4][4], F f) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #pragma unroll
-    for (int mi = 0; mi < 2; ++mi)
+    for (int mi = 0; mi < MI; ++mi)
 #pragma unroll
         for (int ni = 0; ni < 4; ++ni) {
             const int col = warp * 32 + ni * 8 + (lane & 3) * 2;

@@ -6,9 +6,9 @@
 //
 //   causal_conv : u[t][c] = bias[c] + sum_k w[c][k] * in[t - (taps-1-k)][c]; inputs before the step's first token
 //                 come from the slot, inputs before the request's start are zero (the slot was zeroed)
-//   gated_scan  : a = exp(-decay * r * softplus(lam)), S <- a S + sqrt(1 - a^2) * (i * u), out = S * gelu_tanh(y);
-//                 one thread per (request, channel) walks the request's tokens of this step in order, then stores S
-//                 and the convolution's newest inputs back into the slot
+//   gated_scan  : a = exp(-decay * r * softplus(lam)), S <- a S + sqrt(1 - a^2) * (i * u), out = S * gelu_tanh(y)
+//                 over a request's tokens of this step in order (in stretches that are scanned side by side and
+//                 joined), then S and the convolution's newest inputs go back into the slot
 // r, i: float32 gates [T][2 * width] laid out per block as [r of the block | i of the block]. Decays, their
 // logarithms, softplus, exponentials and the state are float32; u, y and the output are in the compute dtype.
 #include "common.cuh"
@@ -62,35 +62,79 @@ __device__ __forceinline__ float rc_gelu_tanh(float z) {
     return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
+// A block is 32 channels x 32 stretches of a request's tokens of this step. A recurrence S <- a S + b composes:
+// a stretch is (A, B) = (product of its a, its own scan from zero), so the stretches are scanned side by side, their
+// (A, B) folded in order by the first row of threads, and each stretch scanned again from its true start to write the
+// outputs. A request that brings one token (decoding) is one stretch of one step.
+constexpr int GS_CH = 32, GS_PARTS = 32;
+
 template <typename T>
-__global__ void gated_scan_kernel(T* __restrict__ out, float* __restrict__ state, const T* __restrict__ u,
-                                  const float* __restrict__ gates, const T* __restrict__ yx, int ld_yx, int y_off, int x_off,
-                                  const float* __restrict__ lam, const int* __restrict__ cu_seqlens,
-                                  const int* __restrict__ state_slots, int width, int block_width, int taps, float decay) {
+__global__ void __launch_bounds__(GS_CH * GS_PARTS) gated_scan_kernel(
+    T* __restrict__ out, float* __restrict__ state, const T* __restrict__ u, const float* __restrict__ gates,
+    const T* __restrict__ yx, int ld_yx, int y_off, int x_off, const float* __restrict__ lam,
+    const int* __restrict__ cu_seqlens, const int* __restrict__ state_slots, int width, int block_width, int taps, float decay) {
+    __shared__ float prod[GS_PARTS][GS_CH + 1], own[GS_PARTS][GS_CH + 1], start[GS_PARTS][GS_CH + 1];
     ti_grid_launch_dependents();
     ti_grid_wait();
     const int seq = blockIdx.y;
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= width) return;
+    const int cx = threadIdx.x, part = threadIdx.y;
+    const int c = blockIdx.x * GS_CH + cx;
+    const bool live = c < width;
     const int row0 = cu_seqlens[seq], row1 = cu_seqlens[seq + 1];
+    const int n = row1 - row0;
+    const int len = (n + GS_PARTS - 1) / GS_PARTS;
+    const int t0 = min(row1, row0 + part * len), t1 = min(row1, t0 + len);
     float* slot = state + (size_t)state_slots[seq] * taps * width;
-    const int blk = c / block_width, o = c % block_width;
-    const size_t g_off = (size_t)blk * 2 * block_width + o;      // r; i lies block_width further on
-    const float rate = decay * rc_softplus(lam[c]);
-    float S = slot[c];
-    for (int t = row0; t < row1; ++t) {
+    size_t g_off = 0;
+    float rate = 0.f;
+    if (live) {
+        const int blk = c / block_width, o = c % block_width;
+        g_off = (size_t)blk * 2 * block_width + o;              // r; i lies block_width further on
+        rate = decay * rc_softplus(lam[c]);
+    }
+    auto terms = [&](int t, float& a, float& b) {
         const float r = gates[(size_t)t * 2 * width + g_off];
         const float g = gates[(size_t)t * 2 * width + g_off + block_width];
         const float log_a = -rate * r;
-        const float a = expf(log_a);
+        a = expf(log_a);
         const float mult = sqrtf(fmaxf(-expm1f(2.f * log_a), 0.f));       // sqrt(1 - a^2) without the cancellation
-        S = fmaf(a, S, mult * (g * to_f32(u[(size_t)t * width + c])));
+        b = mult * (g * to_f32(u[(size_t)t * width + c]));
+    };
+    float A = 1.f, B = 0.f;
+    if (live) {
+#pragma unroll 4
+        for (int t = t0; t < t1; ++t) {
+            float a, b;
+            terms(t, a, b);
+            B = fmaf(a, B, b);
+            A *= a;
+        }
+    }
+    prod[part][cx] = A;
+    own[part][cx] = B;
+    __syncthreads();
+    if (part == 0 && live) {
+        float S = slot[c];
+        for (int k = 0; k < GS_PARTS; ++k) {
+            start[k][cx] = S;
+            S = fmaf(prod[k][cx], S, own[k][cx]);
+        }
+        slot[c] = S;
+    }
+    __syncthreads();
+    if (!live) return;
+    float S = start[part][cx];
+#pragma unroll 4
+    for (int t = t0; t < t1; ++t) {
+        float a, b;
+        terms(t, a, b);
+        S = fmaf(a, S, b);
         const float y = rc_gelu_tanh(to_f32(yx[(size_t)t * ld_yx + y_off + c]));
         out[(size_t)t * width + c] = from_f32<T>(S * y);
     }
-    slot[c] = S;
+    if (part != 0) return;
     // the convolution's last taps - 1 inputs: from this step's rows, or, where the step was shorter, moved up
-    const int n = row1 - row0, keep = taps - 1;
+    const int keep = taps - 1;
     float fresh[RC_MAX_TAPS];
     for (int j = 0; j < keep; ++j) {
         const int idx = n - keep + j;                  // local index of the input that becomes entry j
@@ -107,12 +151,12 @@ TI_API int ti_gated_scan(void* out, float* state, const void* u, const float* ga
     TI_REQUIRE(taps >= 1 && taps <= RC_MAX_TAPS, "gated_scan: taps must be 1..%d", RC_MAX_TAPS);
     TI_REQUIRE(num_seqs <= 65535, "gated_scan: too many requests");
     if (num_seqs == 0) return 0;
-    dim3 grid((width + 63) / 64, num_seqs);
+    dim3 grid((width + GS_CH - 1) / GS_CH, num_seqs), block(GS_CH, GS_PARTS);
     if (dtype == TI_F32)
-        ti_launch(gated_scan_kernel<float>, grid, 64, 0, stream, (float*)out, state, (const float*)u, gates, (const float*)yx,
+        ti_launch(gated_scan_kernel<float>, grid, block, 0, stream, (float*)out, state, (const float*)u, gates, (const float*)yx,
                   ld_yx, y_off, x_off, lam, cu_seqlens, state_slots, width, block_width, taps, decay);
     else if (dtype == TI_BF16)
-        ti_launch(gated_scan_kernel<__nv_bfloat16>, grid, 64, 0, stream, (__nv_bfloat16*)out, state, (const __nv_bfloat16*)u, gates,
+        ti_launch(gated_scan_kernel<__nv_bfloat16>, grid, block, 0, stream, (__nv_bfloat16*)out, state, (const __nv_bfloat16*)u, gates,
                   (const __nv_bfloat16*)yx, ld_yx, y_off, x_off, lam, cu_seqlens, state_slots, width, block_width, taps, decay);
     else TI_REQUIRE(false, "gated_scan: unknown dtype %d", dtype);
     TI_CHECK_LAUNCH("gated_scan");

@@ -70,8 +70,9 @@ _SIGNATURES = {
         "ti_moe_route": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                          c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p],
         "ti_moe_tile_rows": [],
-        "ti_moe_gemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+        "ti_moe_gemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                         c_void_p],
+        "ti_moe_wide_tiles_ok": [c_int, c_int],
         "ti_moe_combine_norm_add": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                     c_int, c_float, c_int, c_void_p],
     },
@@ -920,15 +921,18 @@ class ExpertRouting:
     ``tiles`` int32 [max_tiles, 3] = [expert, first row, rows] with their count ``num_tiles`` int32 [1] (on the
     device: the grouped products are launched for ``max_tiles`` and the surplus returns at once)."""
 
-    def __init__(self, chosen, weight, slot_of, token_of, tiles, num_tiles, max_tiles, counts):
+    def __init__(self, chosen, weight, slot_of, token_of, tiles, num_tiles, max_tiles, counts, tile_rows):
         self.chosen, self.weight, self.slot_of, self.token_of = chosen, weight, slot_of, token_of
         self.tiles, self.num_tiles, self.max_tiles, self.counts = tiles, num_tiles, max_tiles, counts
+        self.tile_rows = tile_rows
 
 
-def route_experts(x32: torch.Tensor, w_router: torch.Tensor, top: int, weight_eps: float) -> ExpertRouting:
+def route_experts(x32: torch.Tensor, w_router: torch.Tensor, top: int, weight_eps: float,
+                  wide_tiles: bool = False) -> ExpertRouting:
     """Router of a mixture of experts: float32 logits from the float32 rows ``x32`` [T, H] and ``w_router`` [E, H],
     softmax over all experts, the ``top`` largest (first index on ties), weights = their scores over their sum
-    (+ ``weight_eps``)."""
+    (+ ``weight_eps``). ``wide_tiles``: the row tiles of the plan hold 64 rows instead of 32 (for steps that bring
+    an expert many rows; only the tensor-core grouped product takes them, see ``expert_tiles_may_be_wide``)."""
     _check(x32, "x32", torch.float32, 2)
     _check(w_router, "w_router", None, 2)
     t, hidden = x32.shape
@@ -936,8 +940,7 @@ def route_experts(x32: torch.Tensor, w_router: torch.Tensor, top: int, weight_ep
     if w_router.shape[1] != hidden:
         raise KernelError("route_experts: the router's rows do not match the stream's")
     dev = x32.device
-    fn = _fn("core", "ti_moe_tile_rows")
-    tile_rows = int(fn())
+    tile_rows = 64 if wide_tiles else int(_fn("core", "ti_moe_tile_rows")())
     max_tiles = (t * top + tile_rows - 1) // tile_rows + experts
     ints = torch.empty(t * top * 4 + experts + (experts + 1) + 3 * max_tiles + 1, dtype=torch.int32, device=dev)
     n = t * top
@@ -952,7 +955,13 @@ def route_experts(x32: torch.Tensor, w_router: torch.Tensor, top: int, weight_ep
          x32.data_ptr(), w_router.data_ptr(), t, hidden, experts, top, float(weight_eps), tile_rows, max_tiles,
          _dtype_code(w_router), _stream())
     return ExpertRouting(chosen.view(t, top), weight, slot_of.view(t, top), token_of, tiles.view(max_tiles, 3),
-                         num_tiles, max_tiles, counts)
+                         num_tiles, max_tiles, counts, tile_rows)
+
+
+def expert_tiles_may_be_wide(x: torch.Tensor, *inner_sizes: int) -> bool:
+    """True if the grouped products of ``x`` [T, K] (and of rows of the given other sizes) run on the tensor cores,
+    which alone take row tiles of 64."""
+    return all(int(_fn("core", "ti_moe_wide_tiles_ok")(k, _dtype_code(x))) for k in (x.shape[1],) + inner_sizes)
 
 
 def expert_linear(x: torch.Tensor, w: torch.Tensor, routing: ExpertRouting, *, up: bool) -> torch.Tensor:
@@ -967,8 +976,8 @@ def expert_linear(x: torch.Tensor, w: torch.Tensor, routing: ExpertRouting, *, u
     slots = routing.token_of.shape[0]
     out = torch.empty((slots, n), dtype=x.dtype if up else torch.float32, device=x.device)
     _run("core", "ti_moe_gemm", out.data_ptr(), x.data_ptr(), w.data_ptr(), routing.tiles.data_ptr(),
-         routing.num_tiles.data_ptr(), routing.token_of.data_ptr(), n, k, routing.max_tiles, int(up), _dtype_code(x),
-         _stream())
+         routing.num_tiles.data_ptr(), routing.token_of.data_ptr(), n, k, routing.max_tiles, routing.tile_rows, int(up),
+         _dtype_code(x), _stream())
     return out
 
 
