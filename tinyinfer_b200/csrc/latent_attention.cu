@@ -261,29 +261,49 @@ __global__ void __launch_bounds__(LA_WARPS * 32) latent_attend_kernel(
     }
 }
 
-// One block per (token, head): folds the parts in key order, then the sink.
+// One block per (token, head): folds the parts in key order, then the sink. The parts' weights exp(m_z - m) are
+// worked out once into shared memory; the features are then one pass of independent loads.
+constexpr int LM_MAX_SPLITS = 64;
+
 template <typename T>
 __global__ void latent_merge_kernel(T* __restrict__ out, const float* __restrict__ parts, const float* __restrict__ sink,
                                     int heads, int rank, int splits) {
+    __shared__ float wz[LM_MAX_SPLITS];
+    __shared__ float inv_l;
     ti_grid_launch_dependents();
     ti_grid_wait();
     const int h = blockIdx.x, t = blockIdx.y;
     const float* src = parts + ((size_t)t * heads + h) * splits * (rank + 2);
-    float m = sink ? sink[h] : -INFINITY;
-    for (int z = 0; z < splits; ++z) m = fmaxf(m, src[(size_t)z * (rank + 2)]);
-    float l = 0.f;
-    for (int z = 0; z < splits; ++z) {
-        const float mz = src[(size_t)z * (rank + 2)];
-        if (mz != -INFINITY) l += src[(size_t)z * (rank + 2) + 1] * expf(mz - m);
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        float mz[LM_MAX_SPLITS / 32], lz[LM_MAX_SPLITS / 32];
+        float m = sink ? sink[h] : -INFINITY;
+#pragma unroll
+        for (int k = 0; k < LM_MAX_SPLITS / 32; ++k) {
+            const int z = lane + 32 * k;
+            mz[k] = z < splits ? src[(size_t)z * (rank + 2)] : -INFINITY;
+            lz[k] = z < splits ? src[(size_t)z * (rank + 2) + 1] : 0.f;
+            m = fmaxf(m, mz[k]);
+        }
+        m = warp_max(m);
+        float l = 0.f;
+#pragma unroll
+        for (int k = 0; k < LM_MAX_SPLITS / 32; ++k) {
+            const int z = lane + 32 * k;
+            const float w = (mz[k] == -INFINITY) ? 0.f : expf(mz[k] - m);
+            if (z < splits) wz[z] = w;
+            l += lz[k] * w;
+        }
+        l = warp_sum(l);
+        if (sink) l += expf(sink[h] - m);
+        if (lane == 0) inv_l = l > 0.f ? 1.f / l : 0.f;
     }
-    if (sink) l += expf(sink[h] - m);
-    const float inv = l > 0.f ? 1.f / l : 0.f;
+    __syncthreads();
+    const float inv = inv_l;
     for (int i = threadIdx.x; i < rank; i += blockDim.x) {
         float a = 0.f;
-        for (int z = 0; z < splits; ++z) {
-            const float mz = src[(size_t)z * (rank + 2)];
-            if (mz != -INFINITY) a += src[(size_t)z * (rank + 2) + 2 + i] * expf(mz - m);
-        }
+#pragma unroll 8
+        for (int z = 0; z < splits; ++z) a = fmaf(src[(size_t)z * (rank + 2) + 2 + i], wz[z], a);
         out[((size_t)t * heads + h) * rank + i] = from_f32<T>(a * inv);
     }
 }
@@ -291,7 +311,8 @@ __global__ void latent_merge_kernel(T* __restrict__ out, const float* __restrict
 // Folds `splits` parts per (token, head) (as the attention kernels leave them) into out [T, heads, rank].
 TI_API int ti_latent_merge(void* out, const float* parts, const float* sink, int num_tokens, int heads, int rank, int splits,
                            int dtype, cudaStream_t stream) {
-    TI_REQUIRE(num_tokens >= 0 && heads > 0 && rank > 0 && splits >= 1 && num_tokens <= 65535, "latent_merge: bad sizes");
+    TI_REQUIRE(num_tokens >= 0 && heads > 0 && rank > 0 && splits >= 1 && splits <= LM_MAX_SPLITS && num_tokens <= 65535,
+               "latent_merge: bad sizes (at most %d splits)", LM_MAX_SPLITS);
     if (num_tokens == 0) return 0;
     dim3 mgrid(heads, num_tokens);
     if (dtype == TI_F32)
@@ -325,7 +346,7 @@ TI_API int ti_latent_attend(void* out, float* parts, long long parts_floats, con
                             float scale, int window, int splits, int* status, int dtype, cudaStream_t stream) {
     TI_REQUIRE(num_tokens >= 0 && heads > 0 && rank > 0 && rot >= 0 && page_size > 0 && window >= 0, "latent_attend: bad sizes");
     TI_REQUIRE(rank <= 512, "latent_attend: a latent of %d features is more than the kernel's 512", rank);
-    TI_REQUIRE(num_tokens <= 65535 && splits >= 1 && splits <= 65535, "latent_attend: too many tokens or splits");
+    TI_REQUIRE(num_tokens <= 65535 && splits >= 1 && splits <= LM_MAX_SPLITS, "latent_attend: too many tokens or splits");
     TI_REQUIRE(splits == 1 || (parts != nullptr && parts_floats >= (long long)num_tokens * heads * splits * (rank + 2)),
                "latent_attend: scratch too small for %d splits", splits);
     if (num_tokens == 0) return 0;

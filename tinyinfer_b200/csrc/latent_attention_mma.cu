@@ -99,16 +99,17 @@ __global__ void __launch_bounds__(128 * MW, 1) latent_attend_mma_kernel(Args a) 
         row_head[tid] = h0 + hl;
     }
     __syncthreads();
-    // the query rows, rounded to bfloat16
-    for (int i = tid; i < ROWS * (dkp / 2); i += THREADS) {
-        const int r = i / (dkp / 2), c = (i % (dkp / 2)) * 2;
-        float v0 = 0.f, v1 = 0.f;
-        if (row_tok[r] >= 0) {
-            const float* src = a.q + ((size_t)row_tok[r] * a.heads + row_head[r]) * dk;
-            if (c < dk) v0 = src[c];
-            if (c + 1 < dk) v1 = src[c + 1];
+    // the query rows, rounded to bfloat16 (dk is a multiple of 8: four features a load)
+    {
+        const int quads = dkp / 4;
+#pragma unroll 4
+        for (int i = tid; i < ROWS * quads; i += THREADS) {
+            const int r = i / quads, c = (i % quads) * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (row_tok[r] >= 0 && c < dk)
+                v = *reinterpret_cast<const float4*>(a.q + ((size_t)row_tok[r] * a.heads + row_head[r]) * dk + c);
+            *reinterpret_cast<uint2*>(Qs + r * lds + c) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
         }
-        *reinterpret_cast<unsigned*>(Qs + r * lds + c) = pack_bf16(v0, v1);
     }
     const int hi = a.positions[tok0 + ntok - 1];              // the block's last token sees the most keys
     int first_key = 0, last_key = hi + 1;

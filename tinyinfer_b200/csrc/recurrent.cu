@@ -65,7 +65,7 @@ __device__ __forceinline__ float rc_gelu_tanh(float z) {
 // A block is 32 channels x 32 stretches of a request's tokens of this step. A recurrence S <- a S + b composes:
 // a stretch is (A, B) = (product of its a, its own scan from zero), so the stretches are scanned side by side, their
 // (A, B) folded in order by the first row of threads, and each stretch scanned again from its true start to write the
-// outputs. A request that brings one token (decoding) is one stretch of one step.
+// outputs. A step of single decoded tokens is launched with one stretch (blockDim.y = 1).
 constexpr int GS_CH = 32, GS_PARTS = 32;
 
 template <typename T>
@@ -82,7 +82,8 @@ __global__ void __launch_bounds__(GS_CH * GS_PARTS) gated_scan_kernel(
     const bool live = c < width;
     const int row0 = cu_seqlens[seq], row1 = cu_seqlens[seq + 1];
     const int n = row1 - row0;
-    const int len = (n + GS_PARTS - 1) / GS_PARTS;
+    const int parts = blockDim.y;
+    const int len = (n + parts - 1) / parts;
     const int t0 = min(row1, row0 + part * len), t1 = min(row1, t0 + len);
     float* slot = state + (size_t)state_slots[seq] * taps * width;
     size_t g_off = 0;
@@ -115,7 +116,7 @@ __global__ void __launch_bounds__(GS_CH * GS_PARTS) gated_scan_kernel(
     __syncthreads();
     if (part == 0 && live) {
         float S = slot[c];
-        for (int k = 0; k < GS_PARTS; ++k) {
+        for (int k = 0; k < parts; ++k) {
             start[k][cx] = S;
             S = fmaf(prod[k][cx], S, own[k][cx]);
         }
@@ -145,13 +146,13 @@ __global__ void __launch_bounds__(GS_CH * GS_PARTS) gated_scan_kernel(
 }
 
 TI_API int ti_gated_scan(void* out, float* state, const void* u, const float* gates, const void* yx, int ld_yx, int y_off,
-                         int x_off, const float* lam, const int* cu_seqlens, const int* state_slots, int num_seqs, int width,
-                         int block_width, int taps, float decay, int dtype, cudaStream_t stream) {
+                         int x_off, const float* lam, const int* cu_seqlens, const int* state_slots, int num_seqs, int num_tokens,
+                         int width, int block_width, int taps, float decay, int dtype, cudaStream_t stream) {
     TI_REQUIRE(num_seqs >= 0 && width > 0 && block_width > 0 && width % block_width == 0, "gated_scan: bad sizes");
     TI_REQUIRE(taps >= 1 && taps <= RC_MAX_TAPS, "gated_scan: taps must be 1..%d", RC_MAX_TAPS);
     TI_REQUIRE(num_seqs <= 65535, "gated_scan: too many requests");
     if (num_seqs == 0) return 0;
-    dim3 grid((width + GS_CH - 1) / GS_CH, num_seqs), block(GS_CH, GS_PARTS);
+    dim3 grid((width + GS_CH - 1) / GS_CH, num_seqs), block(GS_CH, num_tokens == num_seqs ? 1 : GS_PARTS);
     if (dtype == TI_F32)
         ti_launch(gated_scan_kernel<float>, grid, block, 0, stream, (float*)out, state, (const float*)u, gates, (const float*)yx,
                   ld_yx, y_off, x_off, lam, cu_seqlens, state_slots, width, block_width, taps, decay);

@@ -66,7 +66,7 @@ _SIGNATURES = {
         "ti_causal_conv": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                            c_int, c_int, c_int, c_int, c_void_p],
         "ti_gated_scan": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
-                          c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+                          c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
         "ti_moe_route": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                          c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p],
         "ti_moe_tile_rows": [],
@@ -803,7 +803,7 @@ def latent_query_rotate(rows: torch.Tensor, q: torch.Tensor, *, heads: int, plai
          *_rotation_args(rotation), positions.data_ptr(), _dtype_code(q), _stream())
 
 
-LATENT_SPLIT_MIN_KEYS = 256     # a split of the keys over blocks gets at least this many
+LATENT_SPLIT_MIN_KEYS = 128     # a split of the keys over blocks gets at least this many
 LATENT_TARGET_BLOCKS = 296      # enough blocks to have two on every SM
 
 
@@ -909,7 +909,7 @@ def gated_scan(u: torch.Tensor, gates: torch.Tensor, yx: torch.Tensor, *, y_offs
         raise KernelError("gated_scan: shapes do not match")
     out = torch.empty((t, width), dtype=u.dtype, device=u.device)
     _run("core", "ti_gated_scan", out.data_ptr(), state.data_ptr(), u.data_ptr(), gates.data_ptr(), yx.data_ptr(),
-         yx.shape[1], y_offset, x_offset, lam.data_ptr(), cu_seqlens.data_ptr(), state_slots.data_ptr(), num_seqs, width,
+         yx.shape[1], y_offset, x_offset, lam.data_ptr(), cu_seqlens.data_ptr(), state_slots.data_ptr(), num_seqs, t, width,
          block_width, state.shape[1], float(decay), _dtype_code(u), _stream())
     return out
 
