@@ -315,10 +315,11 @@ TI_API int ti_latent_merge(void* out, const float* parts, const float* sink, int
                "latent_merge: bad sizes (at most %d splits)", LM_MAX_SPLITS);
     if (num_tokens == 0) return 0;
     dim3 mgrid(heads, num_tokens);
+    const int threads = rank >= 512 ? 512 : (rank + 31) / 32 * 32;       // a feature a thread
     if (dtype == TI_F32)
-        ti_launch(latent_merge_kernel<float>, mgrid, 128, 0, stream, (float*)out, parts, sink, heads, rank, splits);
+        ti_launch(latent_merge_kernel<float>, mgrid, threads, 0, stream, (float*)out, parts, sink, heads, rank, splits);
     else if (dtype == TI_BF16)
-        ti_launch(latent_merge_kernel<__nv_bfloat16>, mgrid, 128, 0, stream, (__nv_bfloat16*)out, parts, sink, heads, rank, splits);
+        ti_launch(latent_merge_kernel<__nv_bfloat16>, mgrid, threads, 0, stream, (__nv_bfloat16*)out, parts, sink, heads, rank, splits);
     else TI_REQUIRE(false, "latent_merge: unknown dtype %d", dtype);
     TI_CHECK_LAUNCH("latent_merge");
     return 0;
@@ -365,13 +366,6 @@ TI_API int ti_latent_attend(void* out, float* parts, long long parts_floats, con
 #undef LA_GO
     TI_REQUIRE(e == cudaSuccess, "latent_attend: %s", cudaGetErrorString(e));
     TI_CHECK_LAUNCH("latent_attend");
-    if (splits > 1) {
-        dim3 mgrid(heads, num_tokens);
-        if (dtype == TI_F32)
-            ti_launch(latent_merge_kernel<float>, mgrid, 128, 0, stream, (float*)out, (const float*)parts, sink, heads, rank, splits);
-        else
-            ti_launch(latent_merge_kernel<__nv_bfloat16>, mgrid, 128, 0, stream, (__nv_bfloat16*)out, (const float*)parts, sink, heads, rank, splits);
-        TI_CHECK_LAUNCH("latent_merge");
-    }
+    if (splits > 1) return ti_latent_merge(out, parts, sink, num_tokens, heads, rank, splits, dtype, stream);
     return 0;
 }

@@ -3,10 +3,10 @@
 //
 // The rows of a block's query tile are (token, head) pairs: every head of a token reads the same cached rows
 // [c | k_rot], so the heads fill the 16-row tiles of mma.sync that a single token's head could not. A block of
-// 4 MW warps holds 16 MW rows: MW = 4 for prompt portions (with 16 heads: four consecutive tokens of one request),
+// 4 MW warps holds 16 MW rows: MW = 2 for prompt portions (with 16 heads: two consecutive tokens of one request),
 // MW = 1 for decoded tokens (one token's heads; the keys may be shared out over grid z, the parts folded by the
 // merge kernel of latent_attention.cu). Warp (mw, nw) owns rows [16 mw, +16) and, of the value features, the
-// quarter nw. Per tile of 32 cached rows (cp.async, two buffers):
+// quarter nw. Per tile of 32 cached rows (fetched with cp.async):
 //   S  = Q K^T : each warp takes a quarter of the feature range for all 32 keys (its A fragments stay the same for
 //                every tile, its B fragments come with ldmatrix from the key tile) and leaves a partial sum in shared
 //                memory; after a barrier every warp adds the four partials of its rows,
@@ -45,16 +45,18 @@ struct Args {
     int* status;
 };
 
-// NT: 8-column tiles of the value features a warp accumulates (the padded rank is 32 NT).
-template <int MW, int NT>
-__global__ void __launch_bounds__(128 * MW, 1) latent_attend_mma_kernel(Args a) {
+// NT: 8-column tiles of the value features a warp accumulates (the padded rank is 32 NT). KBUF: key-tile buffers
+// (2: the next tile is fetched while this one is worked on; 1: two blocks share an SM instead, and one block's
+// products run while the other waits for its tile or is in its softmax). PER_SM: blocks meant to share an SM.
+template <int MW, int NT, int KBUF, int PER_SM>
+__global__ void __launch_bounds__(128 * MW, PER_SM) latent_attend_mma_kernel(Args a) {
     extern __shared__ __align__(16) unsigned char raw[];
     const int dk = a.rank + a.rot;
     const int dkp = a.dkp;                                    // dk padded: a multiple of 64, at least 32 NT
     const int lds = dkp + 8;                                  // halves per row: ldmatrix without bank conflicts
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(raw);                    // [16 MW][lds]
-    __nv_bfloat16* Ks = Qs + 16 * MW * lds;                                       // [2][KEYS][lds]
-    float* Ss = reinterpret_cast<float*>(Ks + 2 * KEYS * lds);                    // [MW][4][16][SPAD]
+    __nv_bfloat16* Ks = Qs + 16 * MW * lds;                                       // [KBUF][KEYS][lds]
+    float* Ss = reinterpret_cast<float*>(Ks + KBUF * KEYS * lds);                    // [MW][4][16][SPAD]
     int* row_tok = reinterpret_cast<int*>(Ss + MW * 4 * 16 * SPAD);               // [16 MW] flat token or -1
     int* row_pos = row_tok + 16 * MW;
     int* row_head = row_pos + 16 * MW;
@@ -158,13 +160,21 @@ __global__ void __launch_bounds__(128 * MW, 1) latent_attend_mma_kernel(Args a) 
     float* s_mine = Ss + ((mw * 4 + nw) * 16) * SPAD;
     const float* s_all = Ss + (mw * 4 * 16) * SPAD;
 
-    if (first_key < last_key) load_tile(first_key, 0);
-    mt::commit();
-    int buf = 0;
-    for (int j0 = first_key; j0 < last_key; j0 += KEYS, buf ^= 1) {
-        if (j0 + KEYS < last_key) load_tile(j0 + KEYS, buf ^ 1);
+    if (KBUF == 2) {
+        if (first_key < last_key) load_tile(first_key, 0);
         mt::commit();
-        mt::wait_group<1>();
+    }
+    int buf = 0;
+    for (int j0 = first_key; j0 < last_key; j0 += KEYS, buf ^= (KBUF - 1)) {
+        if (KBUF == 2) {
+            if (j0 + KEYS < last_key) load_tile(j0 + KEYS, buf ^ 1);
+            mt::commit();
+            mt::wait_group<1>();
+        } else {
+            load_tile(j0, 0);
+            mt::commit();
+            mt::wait_group<0>();
+        }
         __syncthreads();                                       // the tile (and, the first time, Qs) is in shared memory
         const __nv_bfloat16* kt = Ks + buf * KEYS * lds;
         // ---- partial scores: 16 rows x 32 keys over this warp's quarter of the features
@@ -288,9 +298,9 @@ __global__ void __launch_bounds__(128 * MW, 1) latent_attend_mma_kernel(Args a) 
     }
 }
 
-template <int MW, int NT>
+template <int MW, int NT, int KBUF, int PER_SM>
 static cudaError_t launch(const Args& a, dim3 grid, size_t smem, cudaStream_t stream) {
-    auto kernel = latent_attend_mma_kernel<MW, NT>;
+    auto kernel = latent_attend_mma_kernel<MW, NT, KBUF, PER_SM>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     return ti_launch(kernel, grid, 128 * MW, smem, stream, a);
@@ -300,8 +310,8 @@ static cudaError_t launch(const Args& a, dim3 grid, size_t smem, cudaStream_t st
 // 1 if the tensor-core form takes these sizes (the caller then need not try): rows of a multiple of 8 features.
 TI_API int ti_latent_attend_mma_ok(int rank, int rot) { return (rank + rot) % 8 == 0 && rank <= 512 && rank > 0 ? 1 : 0; }
 
-// decode != 0: every token is a block of its own (its heads are the rows); else blocks of 64 rows are dealt to the
-// requests' consecutive tokens. q float32 [T, heads, rank + rot]; out bfloat16 [T, heads, rank].
+// decode != 0: every token is a block of its own (its heads are the rows); else blocks of 32 rows are dealt to the
+// requests' consecutive tokens, two blocks an SM. q float32 [T, heads, rank + rot]; out bfloat16 [T, heads, rank].
 TI_API int ti_latent_attend_mma(void* out, float* parts, long long parts_floats, const float* q, const void* cache,
                                 const float* sink, const int* positions, const int* token_seq, const int* cu_seqlens,
                                 const int* block_table, int max_blocks, int num_seqs, int num_tokens, int heads, int rank,
@@ -313,7 +323,7 @@ TI_API int ti_latent_attend_mma(void* out, float* parts, long long parts_floats,
     TI_REQUIRE(splits == 1 || (parts != nullptr && parts_floats >= (long long)num_tokens * heads * splits * (rank + 2)),
                "latent_attend_mma: scratch too small for %d splits", splits);
     if (num_tokens == 0) return 0;
-    const int mw = decode ? 1 : 4;
+    const int mw = decode ? 1 : 2, kbuf = decode ? 2 : 1;
     const int rows = 16 * mw;
     lm::Args a;
     a.out = (__nv_bfloat16*)out; a.parts = parts; a.q = q; a.cache = (const __nv_bfloat16*)cache; a.sink = sink;
@@ -325,14 +335,14 @@ TI_API int ti_latent_attend_mma(void* out, float* parts, long long parts_floats,
     const int nt = rank <= 128 ? 4 : (rank <= 256 ? 8 : 16);
     const int dkp = ((rank + rot + 63) / 64 * 64) > 32 * nt ? ((rank + rot + 63) / 64 * 64) : 32 * nt, lds = dkp + 8;
     a.dkp = dkp;
-    const size_t smem = (size_t)(rows + 2 * lm::KEYS) * lds * 2 + (size_t)mw * 4 * 16 * lm::SPAD * 4 + (size_t)3 * rows * 4;
+    const size_t smem = (size_t)(rows + kbuf * lm::KEYS) * lds * 2 + (size_t)mw * 4 * 16 * lm::SPAD * 4 + (size_t)3 * rows * 4;
     TI_REQUIRE(smem <= 220 * 1024, "latent_attend_mma: rows of %d features do not fit shared memory", rank + rot);
     const int blocks = a.tpb == 1 ? num_tokens : (num_tokens + a.tpb - 1) / a.tpb + num_seqs;
     dim3 grid(blocks, (heads + a.hpb - 1) / a.hpb, splits);
     TI_REQUIRE(grid.y <= 65535, "latent_attend_mma: too many heads");
     cudaError_t e;
-    if (decode) e = nt == 4 ? lm::launch<1, 4>(a, grid, smem, stream) : nt == 8 ? lm::launch<1, 8>(a, grid, smem, stream) : lm::launch<1, 16>(a, grid, smem, stream);
-    else e = nt == 4 ? lm::launch<4, 4>(a, grid, smem, stream) : nt == 8 ? lm::launch<4, 8>(a, grid, smem, stream) : lm::launch<4, 16>(a, grid, smem, stream);
+    if (decode) e = nt == 4 ? lm::launch<1, 4, 2, 2>(a, grid, smem, stream) : nt == 8 ? lm::launch<1, 8, 2, 2>(a, grid, smem, stream) : lm::launch<1, 16, 2, 2>(a, grid, smem, stream);
+    else e = nt == 4 ? lm::launch<2, 4, 1, 2>(a, grid, smem, stream) : nt == 8 ? lm::launch<2, 8, 1, 2>(a, grid, smem, stream) : lm::launch<2, 16, 1, 2>(a, grid, smem, stream);
     TI_REQUIRE(e == cudaSuccess, "latent_attend_mma: %s", cudaGetErrorString(e));
     TI_CHECK_LAUNCH("latent_attend_mma");
     return 0;

@@ -848,7 +848,7 @@ def latent_attention(q_rows: torch.Tensor, cache: torch.Tensor, *, heads: int, r
     if (step is not None and cache.dtype == torch.bfloat16 and not window
             and int(_fn("core", "ti_latent_attend_mma_ok")(rank, rot))):
         decode = step.max_q_len == 1
-        rows = 16 if decode else 64
+        rows = 16 if decode else 32
         per_block = min(heads, rows)
         tokens_per_block = 1 if decode else max(1, rows // per_block)
         splits = share_out(-(-t // tokens_per_block) * -(-heads // per_block))
