@@ -264,3 +264,27 @@ def test_greedy_generation_through_the_scheduler(tmp_path, dtype, tol):
     assert not llm.runner.manager.live_requests
     llm.runner.manager.check_consistency()
     llm.close()
+
+
+def test_command_line_generates_with_a_folder_and_with_a_preset(tmp_path):
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    folder = gh.write_folder(tmp_path / "m", gh.MIX, seed=3)
+    common = ["--dtype", "fp32", "--prompt-ids", "5,17,3,200", "--prompt-len", "9", "--greedy", "--max-tokens", "6",
+              "--max-num-seqs", "2", "--max-num-batched-tokens", "16", "--block-size", "4", "--num-kvcache-blocks", "32",
+              "--max-model-len", "64"]
+    res = subprocess.run([sys.executable, str(root / "examples" / "generate.py"), "--model", str(folder)] + common,
+                         capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stderr[-2000:]
+    rows = [json.loads(l) for l in res.stdout.splitlines() if l.startswith("{")]
+    assert len(rows) == 2 and all(len(r["token_ids"]) == 6 for r in rows)
+    c, w = gh.read_folder(folder)
+    logits = plain.forward(c, w, [5, 17, 3, 200] + rows[0]["token_ids"]).numpy()
+    for i, tok in enumerate(rows[0]["token_ids"]):
+        assert logits[3 + i].max() - logits[3 + i][tok] <= 1e-4 * np.abs(logits).max()
+    res = subprocess.run([sys.executable, str(root / "examples" / "generate.py"), "--random-config", "gulisun-tiny"] + common,
+                         capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stderr[-2000:]

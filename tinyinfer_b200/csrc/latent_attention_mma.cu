@@ -123,28 +123,29 @@ __global__ void __launch_bounds__(128 * MW, PER_SM) latent_attend_mma_kernel(Arg
     const int* table = a.block_table + (size_t)seq * a.max_blocks;
     const int chunks = dkp / 8;                                // 16-byte pieces of a row in shared memory
     const int real_chunks = dk / 8;
-    // a warp fetches whole rows: the row's page is looked up once, its 16-byte pieces go a lane apiece
+    // a warp fetches whole rows, their 16-byte pieces a lane apiece; where a row lies is worked out once a tile,
+    // lane l for key j0 + l (one division and one look-up in the block table a lane), and handed round by shuffle
     auto load_tile = [&](int j0, int buf) {
         __nv_bfloat16* dst = Ks + buf * KEYS * lds;
         constexpr int PER_WARP = KEYS / (4 * MW);
-        const __nv_bfloat16* src[PER_WARP];
-#pragma unroll
-        for (int i = 0; i < PER_WARP; ++i) {
-            const int key = j0 + warp * PER_WARP + i;
-            src[i] = nullptr;
+        const __nv_bfloat16* mine = nullptr;
+        {
+            const int key = j0 + lane;
             if (key < last_key) {
                 const int logical = key / a.page_size;
                 const int page = logical < a.max_blocks ? table[logical] : -1;
-                if (page >= 0 && page < a.num_pages) src[i] = a.cache + ((size_t)page * a.page_size + key % a.page_size) * dk;
-                else if (lane == 0 && a.status) atomicExch(a.status, 2);      // a visible key without a page
+                if (page >= 0 && page < a.num_pages) mine = a.cache + ((size_t)page * a.page_size + (key - logical * a.page_size)) * dk;
+                else if (a.status) atomicExch(a.status, 2);      // a visible key without a page
             }
         }
 #pragma unroll
         for (int i = 0; i < PER_WARP; ++i) {
+            const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(
+                __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(mine), warp * PER_WARP + i));
             __nv_bfloat16* row = dst + (warp * PER_WARP + i) * lds;
             for (int c = lane; c < chunks; c += 32) {
-                const bool ok = src[i] != nullptr && c < real_chunks;
-                mt::cp16(row + c * 8, ok ? src[i] + c * 8 : a.cache, ok);
+                const bool ok = src != nullptr && c < real_chunks;
+                mt::cp16(row + c * 8, ok ? src + c * 8 : a.cache, ok);
             }
         }
     };
@@ -184,6 +185,7 @@ __global__ void __launch_bounds__(128 * MW, PER_SM) latent_attend_mma_kernel(Arg
 #pragma unroll
             for (int e = 0; e < 4; ++e) s[ni][e] = 0.f;
         const __nv_bfloat16* k_base = kt + ((lane & 7) + ((lane >> 4) << 3)) * lds + nw * (dkp / 4) + ((lane >> 3) & 1) * 8;
+#pragma unroll 3
         for (int ks = 0; ks < ksteps; ++ks) {
             unsigned af[4], bf[2][4];
             mt::ldmatrix_x4(af, q_base + ks * 16);

@@ -834,9 +834,9 @@ def latent_attention(q_rows: torch.Tensor, cache: torch.Tensor, *, heads: int, r
     if t == 0:
         return out
 
-    def share_out(blocks: int) -> int:
-        if blocks < LATENT_TARGET_BLOCKS and max_context >= 2 * LATENT_SPLIT_MIN_KEYS:
-            return max(1, min(-(-LATENT_TARGET_BLOCKS // blocks), int(max_context) // LATENT_SPLIT_MIN_KEYS, 64))
+    def share_out(blocks: int, least: int = LATENT_SPLIT_MIN_KEYS) -> int:
+        if blocks < LATENT_TARGET_BLOCKS and max_context >= 2 * least:
+            return max(1, min(-(-LATENT_TARGET_BLOCKS // blocks), int(max_context) // least, 64))
         return 1
 
     def scratch(splits: int):
@@ -851,7 +851,7 @@ def latent_attention(q_rows: torch.Tensor, cache: torch.Tensor, *, heads: int, r
         rows = 16 if decode else 32
         per_block = min(heads, rows)
         tokens_per_block = 1 if decode else max(1, rows // per_block)
-        splits = share_out(-(-t // tokens_per_block) * -(-heads // per_block))
+        splits = share_out(-(-t // tokens_per_block) * -(-heads // per_block), 64 if decode else LATENT_SPLIT_MIN_KEYS)
         parts, parts_floats = scratch(splits)
         _run("core", "ti_latent_attend_mma", out.data_ptr(), _ptr(parts), parts_floats, q_rows.data_ptr(), cache.data_ptr(),
              _ptr(sink), positions.data_ptr(), token_seq.data_ptr(), step.cu_seqlens.data_ptr(), block_table.data_ptr(),
