@@ -116,8 +116,10 @@ def test_batched_product_against_torch(m, batch, n, k, gap, dtype, tol):
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
-@pytest.mark.parametrize("tokens,experts,top,ff,width", [(1, 4, 2, 24, 40), (150, 6, 3, 136, 64), (77, 9, 1, 40, 72)])
+@pytest.mark.parametrize("tokens,experts,top,ff,width", [(1, 4, 2, 24, 40), (150, 6, 3, 136, 64), (77, 9, 1, 40, 72),
+                                                         (700, 5, 2, 192, 128), (333, 3, 3, 320, 64)])
 def test_grouped_expert_products_against_torch(tokens, experts, top, ff, width, dtype, tol):
+    """The last two shapes bring an expert enough rows for the tcgen05 form (bfloat16) and row tiles of 128."""
     from tinyinfer_b200 import ops
     gen = torch.Generator().manual_seed(tokens)
     x = torch.randn(tokens, width, generator=gen)
@@ -125,7 +127,10 @@ def test_grouped_expert_products_against_torch(tokens, experts, top, ff, width, 
     up = (torch.randn(experts, ff, width, generator=gen) / width ** 0.5).to(dtype)
     down = (torch.randn(experts, width, ff, generator=gen) / ff ** 0.5).to(dtype)
     xc = x.to(dtype)
-    routing = ops.route_experts(x.cuda(), router.cuda(), top, 1e-20)
+    routing = ops.route_experts(x.cuda(), router.cuda(), top, 1e-20,
+                                tile_rows=ops.expert_tile_rows(xc.cuda(), experts, top, ff))
+    if tokens * top >= 96 * experts:
+        assert routing.tile_rows == (128 if dtype == torch.bfloat16 else 32)
     hidden = ops.expert_linear(xc.cuda(), up.cuda(), routing, up=True)
     out = ops.expert_linear(hidden, down.cuda(), routing, up=False).cpu()
     chosen, slot_of = routing.chosen.cpu().long(), routing.slot_of.cpu().long()
@@ -288,3 +293,54 @@ def test_command_line_generates_with_a_folder_and_with_a_preset(tmp_path):
     res = subprocess.run([sys.executable, str(root / "examples" / "generate.py"), "--random-config", "gulisun-tiny"] + common,
                          capture_output=True, text=True, timeout=600)
     assert res.returncode == 0, res.stderr[-2000:]
+
+
+def random_config(seed):
+    """A model of random sizes and layer order: odd head counts, ranks that are no multiple of 8 or 32, one to four
+    experts a token, convolutions of two to six taps, a width that the tensor-core products refuse now and then."""
+    import random
+    rng = random.Random(seed)
+    width = rng.choice([40, 72, 100, 136])
+    layers, writers = [], []
+    for i in range(rng.randint(3, 6)):
+        kind = rng.choice(["latent_attention", "latent_attention_2", "rglru", "reader"])
+        if kind == "reader" and not writers:
+            kind = "latent_attention"
+        if kind == "rglru":
+            blocks = rng.choice([1, 2, 3, 4])
+            mixer = dict(width=blocks * rng.choice([8, 12, 20, 32]), blocks=blocks, conv=rng.randint(2, 6))
+            kind_name = "rglru"
+        elif kind == "reader":
+            j = rng.choice(writers)
+            src = layers[j]["mixer"]
+            mixer = gh.latent(rng.randint(1, 9), rng.choice([8, 12, 24]), src["rot_dim"], rng.choice([8, 20, 32]),
+                              rng.choice([16, 28, 40]), src["kv_rank"], scale=rng.uniform(0.1, 0.4), base=src["rot"]["base"], kv_from=j)
+            kind_name = "latent_attention"
+        else:
+            mixer = gh.latent(rng.randint(1, 9), rng.choice([8, 12, 24, 40]), rng.choice([4, 8, 16, 24]), rng.choice([8, 20, 32, 48]),
+                              rng.choice([16, 28, 40, 64]), rng.choice([24, 40, 56, 100, 136]), scale=rng.uniform(0.1, 0.4),
+                              base=rng.choice([100.0, 10000.0, 1e6]))
+            kind_name = kind
+            writers.append(i)
+        experts = rng.randint(2, 20)
+        mlp = None if rng.random() < 0.2 else gh.moe(experts, rng.randint(1, min(4, experts)), rng.choice([8, 24, 40]),
+                                                     shared=rng.choice([None, 16, 56]))
+        layers.append(dict(type=kind_name, mixer=mixer, mlp=mlp))
+    return gh.config(layers, vocab=rng.choice([97, 256, 300]), width=width, scale=rng.choice([1.0, 4.0, 11.0]),
+                     eps=rng.choice([1e-5, 1e-6]))
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3, 4, 5, 6])
+def test_models_of_random_sizes_and_orders(tmp_path, seed):
+    cfg = random_config(seed)
+    page = [4, 8, 16, 32, 64, 16][seed - 1]
+    requests = gh.random_requests(cfg, [70, 1, 37, 150, 2, 64], seed=seed)
+    folder = gh.write_folder(tmp_path / "m", cfg, seed=seed)
+    want = gh.plain_logits(folder, requests)
+    for steps in (helpers.trace_whole(requests), helpers.trace_mixed(requests, seed=seed, max_live=3, decode_tail=20)):
+        got, _ = run(folder, "float32", steps, page, max_live=3)
+        assert helpers.first_bad(got, want, TOL["float32"]) is None, cfg
+    folder16 = gh.write_folder(tmp_path / "m16", cfg, seed=seed, dtype="bfloat16")
+    got, _ = run(folder16, "bfloat16", helpers.trace_mixed(requests, seed=seed, max_live=3, decode_tail=20), page, max_live=3)
+    err = row_errors(got, gh.plain_logits(folder16, requests))
+    assert np.isfinite(err).all() and np.median(err) <= TOL["bfloat16"] / 2, (np.median(err), cfg)

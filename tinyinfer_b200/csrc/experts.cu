@@ -307,6 +307,35 @@ TI_API int ti_moe_gemm(void* out, const void* x, const void* w, const int* tiles
     return 0;
 }
 
+// ------------------------------------------------------------------ rows into expert order
+// out[slot] = x[token_of[slot]]: the sorted copy that a product with tiled operand copies reads (a row a warp).
+template <typename T>
+__global__ void moe_gather_kernel(T* __restrict__ out, const T* __restrict__ x, const int* __restrict__ token_of, int slots, int K) {
+    ti_grid_launch_dependents();
+    ti_grid_wait();
+    const int slot = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (slot >= slots) return;
+    const T* src = x + (size_t)token_of[slot] * K;
+    T* dst = out + (size_t)slot * K;
+    constexpr int VEC = 16 / sizeof(T);
+    if (K % VEC == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+        for (int i = lane; i < K / VEC; i += 32) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+    } else {
+        for (int i = lane; i < K; i += 32) dst[i] = src[i];
+    }
+}
+
+TI_API int ti_moe_gather(void* out, const void* x, const int* token_of, int slots, int K, int dtype, cudaStream_t stream) {
+    TI_REQUIRE(slots >= 0 && K > 0, "moe_gather: bad sizes");
+    if (slots == 0) return 0;
+    const int blocks = (slots + 7) / 8;
+    if (dtype == TI_F32) ti_launch(moe_gather_kernel<float>, blocks, 256, 0, stream, (float*)out, (const float*)x, token_of, slots, K);
+    else if (dtype == TI_BF16) ti_launch(moe_gather_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)x, token_of, slots, K);
+    else TI_REQUIRE(false, "moe_gather: unknown dtype %d", dtype);
+    TI_CHECK_LAUNCH("moe_gather");
+    return 0;
+}
+
 // ------------------------------------------------------------------ combine + norm + residual
 template <typename T>
 __global__ void moe_combine_norm_add_kernel(float* __restrict__ x32, T* __restrict__ copy, const float* __restrict__ down,

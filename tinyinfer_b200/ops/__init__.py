@@ -73,6 +73,7 @@ _SIGNATURES = {
         "ti_moe_gemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                         c_void_p],
         "ti_moe_wide_tiles_ok": [c_int, c_int],
+        "ti_moe_gather": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "ti_moe_combine_norm_add": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                     c_int, c_float, c_int, c_void_p],
     },
@@ -85,6 +86,10 @@ _SIGNATURES["sm100"] = {
                             c_void_p, c_void_p, c_void_p, c_void_p],
 }
 _SIGNATURES["sm100"]["ti_gemm_set_pair_form"] = [c_int]
+_SIGNATURES["sm100"]["ti_moe_gemm_tcgen05_ok"] = [c_int, c_int, c_int, c_int]
+_SIGNATURES["sm100"]["ti_moe_tcgen05_tile_rows"] = []
+_SIGNATURES["sm100"]["ti_moe_gemm_tcgen05"] = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                               c_int, c_void_p, c_void_p]
 _SIGNATURES["sm100"]["ti_gemm_pair_bf16"] = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                              c_int, c_void_p, c_void_p]
 NORM_LINK_MAX_TOKENS = 64   # up to here two products can share an RMSNorm between them (see linear)
@@ -928,11 +933,12 @@ class ExpertRouting:
 
 
 def route_experts(x32: torch.Tensor, w_router: torch.Tensor, top: int, weight_eps: float,
-                  wide_tiles: bool = False) -> ExpertRouting:
+                  wide_tiles: bool = False, tile_rows: int = 0) -> ExpertRouting:
     """Router of a mixture of experts: float32 logits from the float32 rows ``x32`` [T, H] and ``w_router`` [E, H],
     softmax over all experts, the ``top`` largest (first index on ties), weights = their scores over their sum
     (+ ``weight_eps``). ``wide_tiles``: the row tiles of the plan hold 64 rows instead of 32 (for steps that bring
-    an expert many rows; only the tensor-core grouped product takes them, see ``expert_tiles_may_be_wide``)."""
+    an expert many rows; only the tensor-core grouped product takes them, see ``expert_tiles_may_be_wide``);
+    ``tile_rows``: any other height the caller has settled with the grouped product (``expert_tile_rows``)."""
     _check(x32, "x32", torch.float32, 2)
     _check(w_router, "w_router", None, 2)
     t, hidden = x32.shape
@@ -940,7 +946,7 @@ def route_experts(x32: torch.Tensor, w_router: torch.Tensor, top: int, weight_ep
     if w_router.shape[1] != hidden:
         raise KernelError("route_experts: the router's rows do not match the stream's")
     dev = x32.device
-    tile_rows = 64 if wide_tiles else int(_fn("core", "ti_moe_tile_rows")())
+    tile_rows = tile_rows or (64 if wide_tiles else int(_fn("core", "ti_moe_tile_rows")()))
     max_tiles = (t * top + tile_rows - 1) // tile_rows + experts
     ints = torch.empty(t * top * 4 + experts + (experts + 1) + 3 * max_tiles + 1, dtype=torch.int32, device=dev)
     n = t * top
@@ -964,6 +970,22 @@ def expert_tiles_may_be_wide(x: torch.Tensor, *inner_sizes: int) -> bool:
     return all(int(_fn("core", "ti_moe_wide_tiles_ok")(k, _dtype_code(x))) for k in (x.shape[1],) + inner_sizes)
 
 
+EXPERT_TCGEN05_MIN_ROWS = 96     # rows an expert gets on average from which the tcgen05 grouped product is used
+
+
+def expert_tile_rows(x: torch.Tensor, num_experts: int, top: int, *inner_sizes: int) -> int:
+    """The height of the row tiles that the grouped products of a step should be planned with: 128 (tcgen05: many
+    rows an expert, bfloat16, whole k blocks of 64), 64 or 32 (the warp-level tensor-core tiles; 32 also float32)."""
+    t = x.shape[0]
+    if x.dtype == torch.bfloat16 and t * top >= EXPERT_TCGEN05_MIN_ROWS * num_experts:
+        ok = _fn("sm100", "ti_moe_gemm_tcgen05_ok")
+        if all(int(ok(t * top, num_experts, n, k)) for n, k in ((inner_sizes[0], x.shape[1]), (x.shape[1], inner_sizes[0]))):
+            return int(_fn("sm100", "ti_moe_tcgen05_tile_rows")())
+    if t * top >= 48 * num_experts and expert_tiles_may_be_wide(x, *inner_sizes):
+        return 64
+    return int(_fn("core", "ti_moe_tile_rows")())
+
+
 def expert_linear(x: torch.Tensor, w: torch.Tensor, routing: ExpertRouting, *, up: bool) -> torch.Tensor:
     """Grouped product over the routing's row tiles with ``w`` [E, N, K]. ``up``: ``x`` [T, K] are the step's
     tokens, gathered per expert; the result [T * top, N] (sorted rows) has passed max(v, 0)^2. Otherwise ``x``
@@ -975,6 +997,16 @@ def expert_linear(x: torch.Tensor, w: torch.Tensor, routing: ExpertRouting, *, u
         raise KernelError("expert_linear: x and w do not match")
     slots = routing.token_of.shape[0]
     out = torch.empty((slots, n), dtype=x.dtype if up else torch.float32, device=x.device)
+    if routing.tile_rows == 128:                 # tcgen05: tiled operand copies want the rows in expert order
+        rows = x
+        if up:
+            rows = torch.empty((slots, k), dtype=x.dtype, device=x.device)
+            _run("core", "ti_moe_gather", rows.data_ptr(), x.data_ptr(), routing.token_of.data_ptr(), slots, k,
+                 _dtype_code(x), _stream())
+        _run("sm100", "ti_moe_gemm_tcgen05", out.data_ptr(), rows.data_ptr(), w.data_ptr(), routing.tiles.data_ptr(),
+             routing.num_tiles.data_ptr(), slots, w.shape[0], n, k, routing.max_tiles, int(up),
+             kernel_status(x.device).data_ptr(), _stream())
+        return out
     _run("core", "ti_moe_gemm", out.data_ptr(), x.data_ptr(), w.data_ptr(), routing.tiles.data_ptr(),
          routing.num_tiles.data_ptr(), routing.token_of.data_ptr(), n, k, routing.max_tiles, routing.tile_rows, int(up),
          _dtype_code(x), _stream())

@@ -49,9 +49,9 @@ class Experts(FeedForward):
     def _experts(self, x32, x):
         """(routing, float32 sorted rows of the experts' outputs, the shared expert's output or None)."""
         s = self.spec
-        # many rows an expert: row tiles of 64 halve the trips of an expert's weights through the grouped products
-        wide = (x.shape[0] * s.top >= 48 * s.num_experts and ops.expert_tiles_may_be_wide(x, s.expert_size))
-        routing = ops.route_experts(x32, self.w_router, s.top, s.weight_eps, wide_tiles=wide)
+        # the more rows an expert gets, the taller the row tiles its grouped products are planned with
+        routing = ops.route_experts(x32, self.w_router, s.top, s.weight_eps,
+                                    tile_rows=ops.expert_tile_rows(x, s.num_experts, s.top, s.expert_size))
         hidden = ops.expert_linear(x, self.w_up, routing, up=True)
         down = ops.expert_linear(hidden, self.w_down, routing, up=False)
         shared = None
