@@ -5,10 +5,11 @@ from .specs import (AttentionSpec, ExecStep, GatedMLPSpec, LayerSpec, ModelSpec,
                     PositionSpec, TensorNames, default_execution)
 from .qwen3 import Qwen3Config
 from .gulisun import GulisunConfig
+from .ravutar import RavutarConfig
 
 __all__ = [
     "EngineConfig", "parse_dtype", "Architecture", "architecture_of", "known_architectures",
     "known_presets", "load_config", "lookup_architecture", "preset_config", "register_architecture", "AttentionSpec", "ExecStep",
     "GatedMLPSpec", "LayerSpec", "ModelSpec", "NormSpec", "PositionSpec", "TensorNames",
-    "default_execution", "Qwen3Config", "GulisunConfig",
+    "default_execution", "Qwen3Config", "GulisunConfig", "RavutarConfig",
 ]

@@ -116,16 +116,105 @@ class ExpertsSpec:
 
 
 @dataclass(frozen=True)
+class ConvAttentionSpec:
+    """Grouped-query softmax attention without a rotation, whose q, k and v pass a short causal convolution over
+    time (``conv_taps`` taps per channel; 1: none) right after their projections. Keys have ``head_dim`` features,
+    values ``v_dim``. ``query_temperature`` (coef, every): the query at position p is multiplied by
+    1 + coef * ln(floor((p + 1) / every) + 1). ``sink``: a logit whose exponential joins the softmax denominator
+    without a value (0.0 adds one to the sum of exp(score)); None: the ordinary softmax."""
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    v_dim: int
+    scale: float
+    conv_taps: int = 1
+    query_temperature: Optional[Tuple[float, int]] = None
+    sink: Optional[float] = None
+    bias: bool = True
+    window: Optional[int] = None
+    kind: str = "conv_attention"
+
+
+@dataclass(frozen=True)
+class GatedLinearAttentionSpec:
+    """Linear attention with a matrix state per head and a decay per key channel: S <- diag(a) S + k v^T,
+    o = S^T q, a = sigmoid(W_a2 W_a1 h + b)^(1 / tau); q is scaled by ``key_dim`` ** -0.5. Each head's o is divided
+    by its root mean square, weighted by one weight shared by the heads, gated by silu(W_g h) and projected.
+    ``gate_rank``: the inner size of the decay's two projections; 0: whatever the checkpoint's tensors have."""
+    hidden_size: int
+    num_heads: int
+    key_dim: int
+    value_dim: int
+    tau: float
+    norm_eps: float
+    gate_rank: int = 0
+    kind: str = "gated_linear_attention"
+
+
+@dataclass(frozen=True)
+class StateSpaceSpec:
+    """Selective state-space mixer with a scalar decay per head (state-space duality): the input projection
+    gives [z | x | B | C | dt]; x, B and C pass a causal convolution with bias and silu; dt = softplus(dt + dt_bias);
+    S <- exp(-exp(A_log) dt) S + dt B x^T (``state_dim`` x ``head_dim`` per head, B and C shared by the heads of a
+    group), y = S^T C + D x; y * silu(z) is normed in ``norm_groups`` equal parts, weighted and projected."""
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    state_dim: int
+    groups: int
+    conv_taps: int
+    norm_groups: int
+    norm_eps: float
+    kind: str = "state_space"
+
+    @property
+    def inner_size(self) -> int:
+        return self.num_heads * self.head_dim
+
+    @property
+    def conv_size(self) -> int:
+        return self.inner_size + 2 * self.groups * self.state_dim
+
+
+@dataclass(frozen=True)
+class ParallelMixerSpec:
+    """Several mixers side by side on the same input: sum_i scales[i] * branch_i(h). ``prefixes[i]`` is put between
+    the mixer's tensor prefix and branch i's local names."""
+    branches: Tuple[object, ...]
+    scales: Tuple[float, ...]
+    prefixes: Tuple[str, ...]
+    kind: str = "parallel"
+
+
+@dataclass(frozen=True)
+class DenseMLPSpec:
+    """Dense feed-forward without a gate: down(act(up h + b_up)) + b_down. ``activation``: 'gelu' (the exact,
+    erf form) or 'gelu_tanh'."""
+    hidden_size: int
+    intermediate_size: int
+    activation: str = "gelu"
+    bias: bool = True
+    kind: str = "dense_mlp"
+
+
+@dataclass(frozen=True)
 class LayerSpec:
     """One block: which mixer, which feed-forward, their norms and how they are arranged.
     ``arrangement='pre_norm'``: x += mixer(norm1(x)); x += feed_forward(norm2(x)).
     ``arrangement='output_norm'``: x += norm1(mixer(x)); x += norm2(feed_forward(x)), the sums in a float32 stream.
+    ``arrangement='multi_stream'``: the residual is ``streams`` float32 copies; a sublayer reads a mixture of them
+    through its norm and writes back into all of them (``learned_mixing``: the block owns the coefficients
+    ``hc1.*`` for the mixer and ``hc2.*`` for the feed-forward; otherwise all are 1, which with one stream is the
+    pre-norm residual kept in float32).
     ``feed_forward`` None (with ``feed_forward_norm`` None): the block has a mixer only."""
     mixer: object
     feed_forward: object
     mixer_norm: NormSpec
     feed_forward_norm: Optional[NormSpec]
     arrangement: str = "pre_norm"
+    streams: int = 1
+    learned_mixing: bool = False
 
 
 @dataclass(frozen=True)

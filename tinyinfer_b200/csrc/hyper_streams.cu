@@ -1,0 +1,180 @@
+// A residual that is several float32 streams instead of one ("hyper-connections": Zhu et al., 2024). The streams
+// are X [S][T][W] float32. A sublayer reads one mixture of them and writes back into all of them:
+//     u = sum_s c_in[s] X[s]                    h = w * u * rsqrt(mean(u^2) + eps)   (the sublayer's input)
+//     X[t] <- sum_s c_mix[s][t] X[s] + c_out[t] * y        (all streams at once from the old ones; y = sublayer(h))
+// One kernel does a sublayer's write-back AND the next sublayer's read: streams_step first applies the update
+// that the sublayer before left pending (if any), in place, then mixes and norms with the next sublayer's
+// coefficients (if any). A block owns a token's row of every stream; the sums and the norm are float32, the
+// rounding of h to the compute dtype is the only one. With S = 1, c_in = c_mix = c_out = 1 this is the ordinary
+// pre-norm residual kept in float32.
+//   streams_embed : X[s][t] = table[id[t]] for every s
+//   streams_step  : as above; `rows` picks the tokens to work on (the rows whose logits are wanted)
+//   gelu, scale   : the feed-forward's activation on a stored tensor, and a constant factor on float32 logits
+#include "common.cuh"
+
+constexpr int HS_MAX_STREAMS = 8;
+
+template <typename T>
+__global__ void streams_embed_kernel(float* __restrict__ X, const T* __restrict__ table, const int* __restrict__ ids,
+                                     int num_tokens, int width, int vocab, int streams) {
+    ti_grid_launch_dependents();
+    ti_grid_wait();
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    const bool ok = id >= 0 && id < vocab;
+    const T* src = table + (size_t)(ok ? id : 0) * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = ok ? to_f32(src[i]) : 0.f;
+        for (int s = 0; s < streams; ++s) X[((size_t)s * num_tokens + t) * width + i] = v;
+    }
+}
+
+TI_API int ti_streams_embed(float* X, const void* table, const int* ids, int num_tokens, int width, int vocab, int streams,
+                            int dtype, cudaStream_t stream) {
+    TI_REQUIRE(num_tokens >= 0 && width > 0 && vocab > 0 && streams >= 1 && streams <= HS_MAX_STREAMS,
+               "streams_embed: bad sizes (1..%d streams)", HS_MAX_STREAMS);
+    if (num_tokens == 0) return 0;
+    const int threads = width >= 1024 ? 256 : 128;
+    if (dtype == TI_F32)
+        ti_launch(streams_embed_kernel<float>, num_tokens, threads, 0, stream, X, (const float*)table, ids, num_tokens, width, vocab, streams);
+    else if (dtype == TI_BF16)
+        ti_launch(streams_embed_kernel<__nv_bfloat16>, num_tokens, threads, 0, stream, X, (const __nv_bfloat16*)table, ids, num_tokens, width, vocab, streams);
+    else TI_REQUIRE(false, "streams_embed: unknown dtype %d", dtype);
+    TI_CHECK_LAUNCH("streams_embed");
+    return 0;
+}
+
+// TY: what the pending sublayer output y is stored in; TH: what h is stored in.
+template <typename TY, typename TH>
+__global__ void streams_step_kernel(float* __restrict__ X, const TY* __restrict__ y, const float* __restrict__ c_mix,
+                                    const float* __restrict__ c_out, const float* __restrict__ c_in,
+                                    const float* __restrict__ norm_w, float eps, TH* __restrict__ h,
+                                    const int* __restrict__ rows, int num_tokens, int width, int streams) {
+    extern __shared__ float urow[];
+    __shared__ float red[33];
+    __shared__ float mix[HS_MAX_STREAMS * HS_MAX_STREAMS], cout_s[HS_MAX_STREAMS], cin_s[HS_MAX_STREAMS];
+    ti_grid_launch_dependents();
+    if (threadIdx.x < streams * streams && y) mix[threadIdx.x] = c_mix[threadIdx.x];      // weights: not written by a kernel
+    if (threadIdx.x < streams) {
+        if (y) cout_s[threadIdx.x] = c_out[threadIdx.x];
+        if (h) cin_s[threadIdx.x] = c_in[threadIdx.x];
+    }
+    ti_grid_wait();
+    __syncthreads();
+    const int r = blockIdx.x;
+    const int t = rows ? rows[r] : r;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float x[HS_MAX_STREAMS];
+#pragma unroll
+        for (int s = 0; s < HS_MAX_STREAMS; ++s)
+            if (s < streams) x[s] = X[((size_t)s * num_tokens + t) * width + i];
+        if (y) {
+            const float yv = to_f32(y[(size_t)t * width + i]);
+            float fresh[HS_MAX_STREAMS];
+#pragma unroll
+            for (int to = 0; to < HS_MAX_STREAMS; ++to) {
+                if (to < streams) {
+                    float acc = 0.f;
+#pragma unroll
+                    for (int s = 0; s < HS_MAX_STREAMS; ++s)
+                        if (s < streams) acc = fmaf(mix[s * streams + to], x[s], acc);
+                    fresh[to] = fmaf(cout_s[to], yv, acc);
+                }
+            }
+#pragma unroll
+            for (int s = 0; s < HS_MAX_STREAMS; ++s)
+                if (s < streams) {
+                    x[s] = fresh[s];
+                    X[((size_t)s * num_tokens + t) * width + i] = fresh[s];
+                }
+        }
+        if (h) {
+            float u = 0.f;
+#pragma unroll
+            for (int s = 0; s < HS_MAX_STREAMS; ++s)
+                if (s < streams) u = fmaf(cin_s[s], x[s], u);
+            urow[i] = u;
+            ss += u * u;
+        }
+    }
+    if (!h) return;
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+        h[(size_t)r * width + i] = from_f32<TH>(norm_w[i] * urow[i] * inv);
+}
+
+// y (may be null: nothing pending) with c_mix [S][S] (indexed [from][to]) and c_out [S]; h (may be null: only the
+// update) with c_in [S] and norm_w [W]. rows (may be null): the tokens to work on; h then has one row per entry.
+TI_API int ti_streams_step(float* X, const void* y, const float* c_mix, const float* c_out, const float* c_in,
+                           const float* norm_w, float eps, void* h, const int* rows, int num_rows, int num_tokens, int width,
+                           int streams, int y_dtype, int h_dtype, cudaStream_t stream) {
+    TI_REQUIRE(num_rows >= 0 && num_tokens >= 0 && width > 0 && streams >= 1 && streams <= HS_MAX_STREAMS,
+               "streams_step: bad sizes (1..%d streams)", HS_MAX_STREAMS);
+    TI_REQUIRE(width <= 48 * 1024 / 4, "streams_step: rows of %d features do not fit shared memory", width);
+    TI_REQUIRE(!y || (c_mix && c_out), "streams_step: an update needs its coefficients");
+    TI_REQUIRE(!h || (c_in && norm_w), "streams_step: a read needs its coefficients and the norm's weight");
+    if (num_rows == 0 || (!y && !h)) return 0;
+    int threads = 64;
+    while (threads < 512 && threads * 4 < width) threads <<= 1;
+    const size_t smem = h ? (size_t)width * sizeof(float) : 0;
+    typedef __nv_bfloat16 B;
+#define TI_STEP(TY, TH)                                                                                              \
+    ti_launch(streams_step_kernel<TY, TH>, num_rows, threads, smem, stream, X, (const TY*)y, c_mix, c_out, c_in, norm_w, \
+              eps, (TH*)h, rows, num_tokens, width, streams)
+    if (y_dtype == TI_F32 && h_dtype == TI_F32) TI_STEP(float, float);
+    else if (y_dtype == TI_F32 && h_dtype == TI_BF16) TI_STEP(float, B);
+    else if (y_dtype == TI_BF16 && h_dtype == TI_BF16) TI_STEP(B, B);
+    else if (y_dtype == TI_BF16 && h_dtype == TI_F32) TI_STEP(B, float);
+    else TI_REQUIRE(false, "streams_step: unknown dtypes %d, %d", y_dtype, h_dtype);
+#undef TI_STEP
+    TI_CHECK_LAUNCH("streams_step");
+    return 0;
+}
+
+// ------------------------------------------------------------------ activation and scaling
+// kind 0: the exact gelu 0.5 z (1 + erf(z / sqrt 2)); 1: its tanh form. In place or not; float32 arithmetic.
+template <typename T>
+__global__ void gelu_kernel(T* __restrict__ out, const T* __restrict__ x, size_t n, int kind) {
+    ti_grid_launch_dependents();
+    ti_grid_wait();
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float z = to_f32(x[i]);
+        const float v = kind == 0 ? 0.5f * z * (1.f + erff(z * 0.70710678118654752f))
+                                  : 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+        out[i] = from_f32<T>(v);
+    }
+}
+
+TI_API int ti_gelu(void* out, const void* x, long long n, int kind, int dtype, cudaStream_t stream) {
+    TI_REQUIRE(n >= 0 && (kind == 0 || kind == 1), "gelu: bad arguments");
+    if (n == 0) return 0;
+    const int threads = 256;
+    const long long want = (n + threads - 1) / threads;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    if (dtype == TI_F32)
+        ti_launch(gelu_kernel<float>, blocks, threads, 0, stream, (float*)out, (const float*)x, (size_t)n, kind);
+    else if (dtype == TI_BF16)
+        ti_launch(gelu_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)x, (size_t)n, kind);
+    else TI_REQUIRE(false, "gelu: unknown dtype %d", dtype);
+    TI_CHECK_LAUNCH("gelu");
+    return 0;
+}
+
+__global__ void scale_kernel(float* __restrict__ x, size_t n, float factor) {
+    ti_grid_launch_dependents();
+    ti_grid_wait();
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) x[i] *= factor;
+}
+
+TI_API int ti_scale(float* x, long long n, float factor, cudaStream_t stream) {
+    TI_REQUIRE(n >= 0, "scale: bad size");
+    if (n == 0) return 0;
+    const long long want = (n + 255) / 256;
+    ti_launch(scale_kernel, (int)(want < 148 * 16 ? want : 148 * 16), 256, 0, stream, x, (size_t)n, factor);
+    TI_CHECK_LAUNCH("scale");
+    return 0;
+}

@@ -1,0 +1,230 @@
+// Linear attention with a decaying matrix state per head, for every mixer of the form
+//     S_t = diag(a_t) S_(t-1) + k_t v_t^T          o_t = S_t^T q_t (+ skip_h * v_t)
+// S is dk x dv per head, float32, kept per request in a state slot (stored transposed, [H][dv][dk], so that a thread's
+// share of a column is contiguous), zero when the request starts. The decay a_t acts on the rows of S (the key
+// channels) and is either one number per key channel or one per head. How it is made from the model's tensors:
+//   gate 0 (raw)          a = gate                                      gate: float32 [T][H * dk] or [T][H]
+//   gate 1 (sigmoid power) a = sigmoid(gate)^(1 / tau) = exp(logsigmoid(gate) / tau), per key channel
+//   gate 2 (step size)     dt = softplus(gate + dt_bias[h]), a = exp(-exp(A_log[h]) * dt) per head, and k_t is
+//                          multiplied by dt (a discretised state-space model: "Transformers are SSMs", Dao and Gu, 2024)
+// Decays, their logarithms, softplus, exponentials, the state and the outputs are float32; q, k and v are read in
+// the compute dtype from wherever they lie (row length and first column given), several heads may share one
+// group of q and k.
+//
+// A block is one request x one head x a few columns of S; a thread holds KPT rows of one column, the rows of a
+// column are spread over KP lanes (row = r * KP + lane part), whose partial sums of o meet by shuffles. The step's
+// tokens of the request are walked in order; q, k and the decays of a few tokens at a time are staged in shared
+// memory by the whole block.
+//
+//   gated_group_norm : out = scale * w * n(y) * silu(gate)  or  scale * w * n(y * silu(gate)),  n: every group of
+//                      `group` features divided by its root mean square (float32), one rounding
+#include "common.cuh"
+
+enum { LS_GATE_RAW = 0, LS_GATE_SIGMOID_POW = 1, LS_GATE_STEP = 2 };
+constexpr int LS_WARPS = 4;
+
+__device__ __forceinline__ float ls_softplus(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
+__device__ __forceinline__ float ls_logsigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
+
+struct LinearScanArgs {
+    float* y;                 // [T][H * dv]
+    float* state;             // slot s at state + s * slot_stride: [H][dv][dk]
+    long long slot_stride;
+    const void *q, *k, *v;    // rows of ld_* elements, first column *_off; q and k: [groups][dk], v: [H][dv]
+    int ld_q, q_off, ld_k, k_off, ld_v, v_off;
+    const float* gate;        // float32 rows of ld_gate, first column gate_off
+    int ld_gate, gate_off, gate_mode, gate_per_channel;
+    float tau;
+    const float *a_log, *dt_bias, *skip;      // [H] each, or null
+    float q_scale;
+    const int *cu_seqlens, *state_slots;
+    int heads, groups, dk, dv, kp, chunk;
+};
+
+template <typename T, int KPT>
+__global__ void __launch_bounds__(LS_WARPS * 32) linear_scan_kernel(LinearScanArgs a) {
+    extern __shared__ float smem[];
+    ti_grid_launch_dependents();
+    ti_grid_wait();
+    const int KP = a.kp, dkp = KP * KPT;                 // dk rounded up to what the lanes hold
+    const int cols_per_warp = 32 / KP, cols_per_block = LS_WARPS * cols_per_warp;
+    const int col_blocks = (a.dv + cols_per_block - 1) / cols_per_block;
+    const int h = blockIdx.x / col_blocks, cb = blockIdx.x % col_blocks;
+    const int seq = blockIdx.y;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int kpart = lane % KP;
+    const int col = cb * cols_per_block + warp * cols_per_warp + lane / KP;
+    const bool col_ok = col < a.dv;
+    const int g = h / (a.heads / a.groups);
+    const int row0 = a.cu_seqlens[seq], row1 = a.cu_seqlens[seq + 1];
+    float* sq = smem;                                    // [chunk][dkp]
+    float* sk = sq + (size_t)a.chunk * dkp;
+    float* sa = sk + (size_t)a.chunk * dkp;
+    float* sv = sa + (size_t)a.chunk * dkp;              // [chunk][cols_per_block]
+    const T* q = (const T*)a.q;
+    const T* k = (const T*)a.k;
+    const T* v = (const T*)a.v;
+
+    float* srow = a.state + (size_t)a.state_slots[seq] * a.slot_stride + ((size_t)h * a.dv + (col_ok ? col : 0)) * a.dk;
+    float S[KPT];
+#pragma unroll
+    for (int r = 0; r < KPT; ++r) {
+        const int idx = r * KP + kpart;
+        S[r] = (col_ok && idx < a.dk) ? srow[idx] : 0.f;
+    }
+    const float skip = a.skip ? a.skip[h] : 0.f;
+    float rate = 0.f, bias = 0.f;
+    if (a.gate_mode == LS_GATE_STEP) {
+        rate = expf(a.a_log[h]);
+        bias = a.dt_bias ? a.dt_bias[h] : 0.f;
+    }
+    const float inv_tau = a.gate_mode == LS_GATE_SIGMOID_POW ? 1.f / a.tau : 0.f;
+
+    for (int t0 = row0; t0 < row1; t0 += a.chunk) {
+        const int n = min(a.chunk, row1 - t0);
+        __syncthreads();                                 // the chunk before has been read
+        for (int e = tid; e < n * dkp; e += LS_WARPS * 32) {
+            const int tt = e / dkp, idx = e % dkp, t = t0 + tt;
+            float qv = 0.f, kv = 0.f, av = 1.f;
+            if (idx < a.dk) {
+                qv = to_f32(q[(size_t)t * a.ld_q + a.q_off + g * a.dk + idx]) * a.q_scale;
+                kv = to_f32(k[(size_t)t * a.ld_k + a.k_off + g * a.dk + idx]);
+                const float gv = a.gate[(size_t)t * a.ld_gate + a.gate_off + (a.gate_per_channel ? h * a.dk + idx : h)];
+                if (a.gate_mode == LS_GATE_RAW) av = gv;
+                else if (a.gate_mode == LS_GATE_SIGMOID_POW) av = expf(ls_logsigmoid(gv) * inv_tau);
+                else {
+                    const float dt = ls_softplus(gv + bias);
+                    av = expf(-rate * dt);
+                    kv *= dt;
+                }
+            }
+            sq[e] = qv;
+            sk[e] = kv;
+            sa[e] = av;
+        }
+        for (int e = tid; e < n * cols_per_block; e += LS_WARPS * 32) {
+            const int tt = e / cols_per_block, c = cb * cols_per_block + e % cols_per_block;
+            sv[e] = c < a.dv ? to_f32(v[(size_t)(t0 + tt) * a.ld_v + a.v_off + h * a.dv + c]) : 0.f;
+        }
+        __syncthreads();
+        for (int tt = 0; tt < n; ++tt) {
+            const float vv = sv[tt * cols_per_block + warp * cols_per_warp + lane / KP];
+            const float* pq = sq + (size_t)tt * dkp + kpart;
+            const float* pk = sk + (size_t)tt * dkp + kpart;
+            const float* pa = sa + (size_t)tt * dkp + kpart;
+            float o = 0.f;
+#pragma unroll
+            for (int r = 0; r < KPT; ++r) {
+                S[r] = fmaf(pa[r * KP], S[r], pk[r * KP] * vv);
+                o = fmaf(S[r], pq[r * KP], o);
+            }
+            for (int off = 1; off < KP; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+            if (kpart == 0 && col_ok) a.y[(size_t)(t0 + tt) * a.heads * a.dv + h * a.dv + col] = fmaf(skip, vv, o);
+        }
+    }
+    if (col_ok) {
+#pragma unroll
+        for (int r = 0; r < KPT; ++r) {
+            const int idx = r * KP + kpart;
+            if (idx < a.dk) srow[idx] = S[r];
+        }
+    }
+}
+
+TI_API int ti_linear_scan(float* y, float* state, long long slot_stride, const void* q, int ld_q, int q_off, const void* k,
+                          int ld_k, int k_off, const void* v, int ld_v, int v_off, const float* gate, int ld_gate,
+                          int gate_off, int gate_mode, int gate_per_channel, float tau, const float* a_log,
+                          const float* dt_bias, const float* skip, float q_scale, const int* cu_seqlens,
+                          const int* state_slots, int num_seqs, int heads, int groups, int dk, int dv, int dtype,
+                          cudaStream_t stream) {
+    TI_REQUIRE(num_seqs >= 0 && heads > 0 && groups > 0 && heads % groups == 0 && dk > 0 && dv > 0, "linear_scan: bad sizes");
+    TI_REQUIRE(dk <= 1024, "linear_scan: %d key channels a head (at most 1024)", dk);
+    TI_REQUIRE(gate_mode >= 0 && gate_mode <= 2 && gate, "linear_scan: unknown gate %d", gate_mode);
+    TI_REQUIRE(gate_mode != LS_GATE_STEP || (a_log && !gate_per_channel), "linear_scan: the step-size gate is one number a head and needs A_log");
+    TI_REQUIRE(gate_mode != LS_GATE_SIGMOID_POW || tau > 0.f, "linear_scan: tau must be positive");
+    TI_REQUIRE(num_seqs <= 65535, "linear_scan: too many requests");
+    if (num_seqs == 0) return 0;
+    // rows of a column over KP lanes, KPT rows a lane: the fewest lanes that keep a lane's share at 16 rows or fewer
+    int kp = 1;
+    while (kp < 32 && (dk + kp - 1) / kp > 16) kp <<= 1;
+    const int per_lane = (dk + kp - 1) / kp;
+    const int kpt = per_lane <= 4 ? 4 : per_lane <= 8 ? 8 : per_lane <= 16 ? 16 : 32;
+    const int dkp = kp * kpt, cols_per_block = LS_WARPS * (32 / kp);
+    int chunk = 16;
+    while (chunk > 1 && (size_t)chunk * (3 * dkp + cols_per_block) * sizeof(float) > 40 * 1024) chunk >>= 1;
+    const size_t smem = (size_t)chunk * (3 * dkp + cols_per_block) * sizeof(float);
+    LinearScanArgs a = {y, state, slot_stride, q, k, v, ld_q, q_off, ld_k, k_off, ld_v, v_off, gate, ld_gate, gate_off,
+                        gate_mode, gate_per_channel, tau, a_log, dt_bias, skip, q_scale, cu_seqlens, state_slots,
+                        heads, groups, dk, dv, kp, chunk};
+    dim3 grid(heads * ((dv + cols_per_block - 1) / cols_per_block), num_seqs);
+    typedef __nv_bfloat16 B;
+#define TI_SCAN(KPT)                                                                                          \
+    do {                                                                                                      \
+        if (dtype == TI_F32) ti_launch(linear_scan_kernel<float, KPT>, grid, LS_WARPS * 32, smem, stream, a); \
+        else ti_launch(linear_scan_kernel<B, KPT>, grid, LS_WARPS * 32, smem, stream, a);                     \
+    } while (0)
+    TI_REQUIRE(dtype == TI_F32 || dtype == TI_BF16, "linear_scan: unknown dtype %d", dtype);
+    if (kpt == 4) TI_SCAN(4);
+    else if (kpt == 8) TI_SCAN(8);
+    else if (kpt == 16) TI_SCAN(16);
+    else TI_SCAN(32);
+#undef TI_SCAN
+    TI_CHECK_LAUNCH("linear_scan");
+    return 0;
+}
+
+// One block per (token, group). gate_first: the gate multiplies y before the norm; otherwise after it.
+template <typename T>
+__global__ void gated_group_norm_kernel(T* __restrict__ out, const float* __restrict__ y, const T* __restrict__ gate,
+                                        int ld_gate, int gate_off, const float* __restrict__ w, int w_len, int width,
+                                        int group, float eps, int gate_first, float out_scale) {
+    __shared__ float red[33];
+    ti_grid_launch_dependents();
+    ti_grid_wait();
+    const int t = blockIdx.x, g0 = blockIdx.y * group;
+    const float* yrow = y + (size_t)t * width + g0;
+    const T* grow = gate ? gate + (size_t)t * ld_gate + gate_off + g0 : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < group; i += blockDim.x) {
+        float v = yrow[i];
+        if (gate_first && grow) {
+            const float z = to_f32(grow[i]);
+            v *= z / (1.f + expf(-z));
+        }
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)group + eps) * out_scale;
+    for (int i = threadIdx.x; i < group; i += blockDim.x) {
+        float v = yrow[i];
+        float gz = 1.f;
+        if (grow) {
+            const float z = to_f32(grow[i]);
+            gz = z / (1.f + expf(-z));
+        }
+        if (gate_first) v *= gz;
+        v = v * inv * w[(g0 + i) % w_len];
+        if (!gate_first) v *= gz;
+        out[(size_t)t * width + g0 + i] = from_f32<T>(v);
+    }
+}
+
+TI_API int ti_gated_group_norm(void* out, const float* y, const void* gate, int ld_gate, int gate_off, const float* w,
+                               int w_len, int num_tokens, int width, int group, float eps, int gate_first, float out_scale,
+                               int dtype, cudaStream_t stream) {
+    TI_REQUIRE(num_tokens >= 0 && width > 0 && group > 0 && width % group == 0 && w_len > 0, "gated_group_norm: bad sizes");
+    TI_REQUIRE(width / group <= 65535, "gated_group_norm: too many groups");
+    if (num_tokens == 0) return 0;
+    int threads = 32;
+    while (threads < 256 && threads < group) threads <<= 1;
+    dim3 grid(num_tokens, width / group);
+    if (dtype == TI_F32)
+        ti_launch(gated_group_norm_kernel<float>, grid, threads, 0, stream, (float*)out, y, (const float*)gate, ld_gate, gate_off,
+                  w, w_len, width, group, eps, gate_first, out_scale);
+    else if (dtype == TI_BF16)
+        ti_launch(gated_group_norm_kernel<__nv_bfloat16>, grid, threads, 0, stream, (__nv_bfloat16*)out, y,
+                  (const __nv_bfloat16*)gate, ld_gate, gate_off, w, w_len, width, group, eps, gate_first, out_scale);
+    else TI_REQUIRE(false, "gated_group_norm: unknown dtype %d", dtype);
+    TI_CHECK_LAUNCH("gated_group_norm");
+    return 0;
+}

@@ -174,13 +174,19 @@ class ModelRunner:
         self.buffers._last = None
         self.storage.kv.clear()
         self.storage.state.clear()
+        def let_go(part):
+            for name, value in list(vars(part).items()):
+                if isinstance(value, torch.Tensor):
+                    setattr(part, name, None)
+                elif isinstance(value, dict) and any(isinstance(v, torch.Tensor) for v in value.values()):
+                    value.clear()
+            for sub in (part.parts() if hasattr(part, "parts") else []):
+                let_go(sub)
+
         for block in self.model.blocks:
-            for part in (block.mixer, block.feed_forward, block.mixer_norm, block.feed_forward_norm):
-                if part is None:
-                    continue
-                for name, value in list(vars(part).items()):
-                    if isinstance(value, torch.Tensor):
-                        setattr(part, name, None)
+            for part in (block, block.mixer, block.feed_forward, block.mixer_norm, block.feed_forward_norm):
+                if part is not None:
+                    let_go(part)
         self.model.embedding = self.model.head = None
         ops.release_scratch(self.device)
         if self.device.type == "cuda":

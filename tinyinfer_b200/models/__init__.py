@@ -1,5 +1,6 @@
 from .decoder import DecoderModel
 from .gulisun import GulisunForCausalLM
 from .qwen3 import Qwen3ForCausalLM
+from .ravutar import RavutarForCausalLM
 
-__all__ = ["DecoderModel", "GulisunForCausalLM", "Qwen3ForCausalLM"]
+__all__ = ["DecoderModel", "GulisunForCausalLM", "Qwen3ForCausalLM", "RavutarForCausalLM"]

@@ -37,7 +37,8 @@ class DecoderModel:
         block = self.blocks[i]
         parts = [(base + n.mixer, block.mixer), (base + n.feed_forward, block.feed_forward),
                  (base + n.mixer_norm, block.mixer_norm),
-                 (base + n.feed_forward_norm, block.feed_forward_norm)]
+                 (base + n.feed_forward_norm, block.feed_forward_norm),
+                 (base, block if block.tensors() else None)]     # tensors of the arrangement itself, if it has any
         return [(prefix, part) for prefix, part in parts if part is not None]     # a block may have a mixer only
 
     def expected_tensors(self) -> Dict[str, TensorSpec]:
@@ -80,7 +81,7 @@ class DecoderModel:
         for name, ts in self.expected_tensors().items():
             n = 1
             for s in ts.shape:
-                n *= s
+                n *= max(s, 0)        # a size only the checkpoint gives counts as nothing
             total += n * (self.dtype.itemsize if ts.role == "matrix" else 4)
         return total
 

@@ -45,6 +45,9 @@ _SIGNATURES = {
         "ti_token_nll": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
         "ti_sample_parts": [],
         "ti_sample_candidates": [],
+    },
+    # the parts of designs with a cached latent, gated recurrences and routed experts
+    "latent": {
         "ti_embedding_scaled": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p],
         "ti_norm_add": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p],
         "ti_rmsnorm_rows32": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
@@ -76,6 +79,29 @@ _SIGNATURES = {
         "ti_moe_gather": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "ti_moe_combine_norm_add": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                     c_int, c_float, c_int, c_void_p],
+    },
+    # parts of designs with several residual streams, short convolutions, attention over [key | value] rows and
+    # linear attention with a matrix state
+    "hybrid": {
+        "ti_streams_embed": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "ti_streams_step": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int,
+                            c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "ti_gelu": [c_void_p, c_void_p, c_ll, c_int, c_int, c_void_p],
+        "ti_scale": [c_void_p, c_ll, c_float, c_void_p],
+        "ti_short_conv": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                          c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "ti_conv_state_update": [c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                 c_void_p],
+        "ti_conv_qkv_append": [c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_void_p, c_int, c_float, c_int, c_void_p,
+                               c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                               c_void_p, c_int, c_void_p],
+        "ti_attention_rows": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                              c_int, c_int, c_int, c_float, c_int, c_int, c_float, c_float, c_void_p, c_int, c_void_p],
+        "ti_linear_scan": [c_void_p, c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
+                           c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_float, c_void_p,
+                           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "ti_gated_group_norm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float,
+                                c_int, c_float, c_int, c_void_p],
     },
 }
 _SIGNATURES["sm100"] = {
@@ -675,7 +701,7 @@ def embedding_scaled(token_ids: torch.Tensor, table: torch.Tensor, scale: float)
     t, hidden = token_ids.shape[0], table.shape[1]
     x32 = torch.empty((t, hidden), dtype=torch.float32, device=table.device)
     copy = None if table.dtype == torch.float32 else torch.empty((t, hidden), dtype=table.dtype, device=table.device)
-    _run("core", "ti_embedding_scaled", x32.data_ptr(), _ptr(copy), table.data_ptr(), token_ids.data_ptr(), t, hidden,
+    _run("latent", "ti_embedding_scaled", x32.data_ptr(), _ptr(copy), table.data_ptr(), token_ids.data_ptr(), t, hidden,
          table.shape[0], float(scale), _dtype_code(table), _stream())
     return x32, (x32 if copy is None else copy)
 
@@ -691,7 +717,7 @@ def norm_add(x32: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: floa
     if y.dtype not in (torch.float32, copy_dtype):
         raise KernelError(f"norm_add: y is {y.dtype}, the stream's copy {copy_dtype}")
     copy = None if copy_dtype == torch.float32 else torch.empty(x32.shape, dtype=copy_dtype, device=x32.device)
-    _run("core", "ti_norm_add", x32.data_ptr(), _ptr(copy), y.data_ptr(), weight.data_ptr(), x32.shape[0], x32.shape[1],
+    _run("latent", "ti_norm_add", x32.data_ptr(), _ptr(copy), y.data_ptr(), weight.data_ptr(), x32.shape[0], x32.shape[1],
          float(eps), _dtype_code(y), 0 if copy is None else _dtype_code(copy), _stream())
     return x32, (x32 if copy is None else copy)
 
@@ -705,7 +731,7 @@ def rmsnorm_rows32(x32: torch.Tensor, weight: torch.Tensor, eps: float, rows: Op
         _check(rows, "rows", torch.int32, 1)
     n = x32.shape[0] if rows is None else rows.shape[0]
     out = torch.empty((n, x32.shape[1]), dtype=out_dtype, device=x32.device)
-    _run("core", "ti_rmsnorm_rows32", out.data_ptr(), x32.data_ptr(), weight.data_ptr(), _ptr(rows), n, x32.shape[1],
+    _run("latent", "ti_rmsnorm_rows32", out.data_ptr(), x32.data_ptr(), weight.data_ptr(), _ptr(rows), n, x32.shape[1],
          float(eps), _dtype_code(out), _stream())
     return out
 
@@ -714,7 +740,7 @@ def relu_squared(x: torch.Tensor) -> torch.Tensor:
     """max(x, 0)^2, one rounding."""
     _check(x, "x")
     out = torch.empty_like(x)
-    _run("core", "ti_relu_squared", out.data_ptr(), x.data_ptr(), x.numel(), _dtype_code(x), _stream())
+    _run("latent", "ti_relu_squared", out.data_ptr(), x.data_ptr(), x.numel(), _dtype_code(x), _stream())
     return out
 
 
@@ -748,7 +774,7 @@ def batched_linear(x: torch.Tensor, w: torch.Tensor, *, x_offset: int = 0, x_bat
         if tuple(bias.shape) != (batch, n):
             raise KernelError("batched_linear: bias must be [B, N]")
     isz_x, isz_o = x.element_size(), out.element_size()
-    _run("core", "ti_gemm_batched", out.data_ptr() + out_offset * isz_o, x.data_ptr() + x_offset * isz_x, w.data_ptr(),
+    _run("latent", "ti_gemm_batched", out.data_ptr() + out_offset * isz_o, x.data_ptr() + x_offset * isz_x, w.data_ptr(),
          _ptr(bias), batch, m, n, k, x.shape[1], x_batch_stride, k, n * k, out.shape[1], out_batch_stride, n,
          int(sigmoid), int(out.dtype == torch.float32 and x.dtype != torch.float32), _dtype_code(x), _stream())
     return out
@@ -788,7 +814,7 @@ def latent_prepare(down: torch.Tensor, *, q_rank: int, rank: int, rot: int, q_no
             raise KernelError(f"latent cache shape {tuple(cache.shape)} is not [1, pages, 1, page, {rank + rot}]")
         num_pages, page_size, max_blocks = cache.shape[1], cache.shape[3], block_table.shape[1]
     out = torch.empty((t, q_rank), dtype=dtype, device=down.device)
-    _run("core", "ti_latent_prepare", out.data_ptr(), _ptr(cache), down.data_ptr(), down.shape[1],
+    _run("latent", "ti_latent_prepare", out.data_ptr(), _ptr(cache), down.data_ptr(), down.shape[1],
          q_norm_weight.data_ptr(), _ptr(kv_norm_weight), float(eps), q_rank, rank, rot, *_rotation_args(rotation),
          positions.data_ptr(), token_seq.data_ptr(), _ptr(block_table) if cache is not None else None, max_blocks, t,
          page_size, num_pages, _ptr(status), _dtype_code(out), _stream())
@@ -804,7 +830,7 @@ def latent_query_rotate(rows: torch.Tensor, q: torch.Tensor, *, heads: int, plai
     _check(positions, "positions", torch.int32, 1)
     if q.shape[1] != heads * (plain + rot) or rows.shape[1] != heads * (rank + rot) or rows.shape[0] != q.shape[0]:
         raise KernelError("latent_query_rotate: widths do not match the head sizes")
-    _run("core", "ti_latent_query", rows.data_ptr(), q.data_ptr(), q.shape[0], heads, plain, rot, rank,
+    _run("latent", "ti_latent_query", rows.data_ptr(), q.data_ptr(), q.shape[0], heads, plain, rot, rank,
          *_rotation_args(rotation), positions.data_ptr(), _dtype_code(q), _stream())
 
 
@@ -851,24 +877,24 @@ def latent_attention(q_rows: torch.Tensor, cache: torch.Tensor, *, heads: int, r
         return parts, parts.numel()
 
     if (step is not None and cache.dtype == torch.bfloat16 and not window
-            and int(_fn("core", "ti_latent_attend_mma_ok")(rank, rot))):
+            and int(_fn("latent", "ti_latent_attend_mma_ok")(rank, rot))):
         decode = step.max_q_len == 1
         rows = 16 if decode else 32
         per_block = min(heads, rows)
         tokens_per_block = 1 if decode else max(1, rows // per_block)
         splits = share_out(-(-t // tokens_per_block) * -(-heads // per_block), 64 if decode else LATENT_SPLIT_MIN_KEYS)
         parts, parts_floats = scratch(splits)
-        _run("core", "ti_latent_attend_mma", out.data_ptr(), _ptr(parts), parts_floats, q_rows.data_ptr(), cache.data_ptr(),
+        _run("latent", "ti_latent_attend_mma", out.data_ptr(), _ptr(parts), parts_floats, q_rows.data_ptr(), cache.data_ptr(),
              _ptr(sink), positions.data_ptr(), token_seq.data_ptr(), step.cu_seqlens.data_ptr(), block_table.data_ptr(),
              block_table.shape[1], step.num_seqs, t, heads, rank, rot, cache.shape[3], cache.shape[1], float(scale), splits,
              int(decode), _ptr(status), _stream())
         if splits > 1:
-            _run("core", "ti_latent_merge", out.data_ptr(), parts.data_ptr(), _ptr(sink), t, heads, rank, splits,
+            _run("latent", "ti_latent_merge", out.data_ptr(), parts.data_ptr(), _ptr(sink), t, heads, rank, splits,
                  _dtype_code(cache), _stream())
         return out
     splits = share_out(t * ((heads + 7) // 8))
     parts, parts_floats = scratch(splits)
-    _run("core", "ti_latent_attend", out.data_ptr(), _ptr(parts), parts_floats, q_rows.data_ptr(), cache.data_ptr(),
+    _run("latent", "ti_latent_attend", out.data_ptr(), _ptr(parts), parts_floats, q_rows.data_ptr(), cache.data_ptr(),
          _ptr(sink), positions.data_ptr(), token_seq.data_ptr(), block_table.data_ptr(), block_table.shape[1], t, heads,
          rank, rot, cache.shape[3], cache.shape[1], float(scale), int(window or 0), splits, _ptr(status),
          _dtype_code(cache), _stream())
@@ -891,7 +917,7 @@ def causal_conv(x: torch.Tensor, *, offset: int, width: int, state: torch.Tensor
     if bias is not None:
         _check(bias, "bias", torch.float32, 1)
     out = torch.empty((x.shape[0], width), dtype=x.dtype, device=x.device)
-    _run("core", "ti_causal_conv", out.data_ptr(), x.data_ptr(), x.shape[1], offset, state.data_ptr(), weight.data_ptr(),
+    _run("latent", "ti_causal_conv", out.data_ptr(), x.data_ptr(), x.shape[1], offset, state.data_ptr(), weight.data_ptr(),
          _ptr(bias), token_seq.data_ptr(), cu_seqlens.data_ptr(), state_slots.data_ptr(), x.shape[0], width, taps,
          _dtype_code(x), _stream())
     return out
@@ -913,7 +939,7 @@ def gated_scan(u: torch.Tensor, gates: torch.Tensor, yx: torch.Tensor, *, y_offs
     if gates.shape != (t, 2 * width) or yx.shape[0] != t or state.shape[2] != width or lam.shape[0] != width:
         raise KernelError("gated_scan: shapes do not match")
     out = torch.empty((t, width), dtype=u.dtype, device=u.device)
-    _run("core", "ti_gated_scan", out.data_ptr(), state.data_ptr(), u.data_ptr(), gates.data_ptr(), yx.data_ptr(),
+    _run("latent", "ti_gated_scan", out.data_ptr(), state.data_ptr(), u.data_ptr(), gates.data_ptr(), yx.data_ptr(),
          yx.shape[1], y_offset, x_offset, lam.data_ptr(), cu_seqlens.data_ptr(), state_slots.data_ptr(), num_seqs, t, width,
          block_width, state.shape[1], float(decay), _dtype_code(u), _stream())
     return out
@@ -946,7 +972,7 @@ def route_experts(x32: torch.Tensor, w_router: torch.Tensor, top: int, weight_ep
     if w_router.shape[1] != hidden:
         raise KernelError("route_experts: the router's rows do not match the stream's")
     dev = x32.device
-    tile_rows = tile_rows or (64 if wide_tiles else int(_fn("core", "ti_moe_tile_rows")()))
+    tile_rows = tile_rows or (64 if wide_tiles else int(_fn("latent", "ti_moe_tile_rows")()))
     max_tiles = (t * top + tile_rows - 1) // tile_rows + experts
     ints = torch.empty(t * top * 4 + experts + (experts + 1) + 3 * max_tiles + 1, dtype=torch.int32, device=dev)
     n = t * top
@@ -956,7 +982,7 @@ def route_experts(x32: torch.Tensor, w_router: torch.Tensor, top: int, weight_ep
     o += 2 * experts + 1
     tiles, num_tiles = ints[o:o + 3 * max_tiles], ints[o + 3 * max_tiles:o + 3 * max_tiles + 1]
     weight = torch.empty((t, top), dtype=torch.float32, device=dev)
-    _run("core", "ti_moe_route", chosen.data_ptr(), weight.data_ptr(), rank.data_ptr(), counts.data_ptr(),
+    _run("latent", "ti_moe_route", chosen.data_ptr(), weight.data_ptr(), rank.data_ptr(), counts.data_ptr(),
          starts.data_ptr(), tiles.data_ptr(), num_tiles.data_ptr(), slot_of.data_ptr(), token_of.data_ptr(),
          x32.data_ptr(), w_router.data_ptr(), t, hidden, experts, top, float(weight_eps), tile_rows, max_tiles,
          _dtype_code(w_router), _stream())
@@ -967,7 +993,7 @@ def route_experts(x32: torch.Tensor, w_router: torch.Tensor, top: int, weight_ep
 def expert_tiles_may_be_wide(x: torch.Tensor, *inner_sizes: int) -> bool:
     """True if the grouped products of ``x`` [T, K] (and of rows of the given other sizes) run on the tensor cores,
     which alone take row tiles of 64."""
-    return all(int(_fn("core", "ti_moe_wide_tiles_ok")(k, _dtype_code(x))) for k in (x.shape[1],) + inner_sizes)
+    return all(int(_fn("latent", "ti_moe_wide_tiles_ok")(k, _dtype_code(x))) for k in (x.shape[1],) + inner_sizes)
 
 
 EXPERT_TCGEN05_MIN_ROWS = 96     # rows an expert gets on average from which the tcgen05 grouped product is used
@@ -983,7 +1009,7 @@ def expert_tile_rows(x: torch.Tensor, num_experts: int, top: int, *inner_sizes: 
             return int(_fn("sm100", "ti_moe_tcgen05_tile_rows")())
     if t * top >= 48 * num_experts and expert_tiles_may_be_wide(x, *inner_sizes):
         return 64
-    return int(_fn("core", "ti_moe_tile_rows")())
+    return int(_fn("latent", "ti_moe_tile_rows")())
 
 
 def expert_linear(x: torch.Tensor, w: torch.Tensor, routing: ExpertRouting, *, up: bool) -> torch.Tensor:
@@ -1001,13 +1027,13 @@ def expert_linear(x: torch.Tensor, w: torch.Tensor, routing: ExpertRouting, *, u
         rows = x
         if up:
             rows = torch.empty((slots, k), dtype=x.dtype, device=x.device)
-            _run("core", "ti_moe_gather", rows.data_ptr(), x.data_ptr(), routing.token_of.data_ptr(), slots, k,
+            _run("latent", "ti_moe_gather", rows.data_ptr(), x.data_ptr(), routing.token_of.data_ptr(), slots, k,
                  _dtype_code(x), _stream())
         _run("sm100", "ti_moe_gemm_tcgen05", out.data_ptr(), rows.data_ptr(), w.data_ptr(), routing.tiles.data_ptr(),
              routing.num_tiles.data_ptr(), slots, w.shape[0], n, k, routing.max_tiles, int(up),
              kernel_status(x.device).data_ptr(), _stream())
         return out
-    _run("core", "ti_moe_gemm", out.data_ptr(), x.data_ptr(), w.data_ptr(), routing.tiles.data_ptr(),
+    _run("latent", "ti_moe_gemm", out.data_ptr(), x.data_ptr(), w.data_ptr(), routing.tiles.data_ptr(),
          routing.num_tiles.data_ptr(), routing.token_of.data_ptr(), n, k, routing.max_tiles, routing.tile_rows, int(up),
          _dtype_code(x), _stream())
     return out
@@ -1024,10 +1050,259 @@ def experts_combine_norm_add(x32: torch.Tensor, down: torch.Tensor, shared_out: 
         _check(shared_out, "shared_out", copy_dtype, 2)
     t, size = x32.shape
     copy = None if copy_dtype == torch.float32 else torch.empty((t, size), dtype=copy_dtype, device=x32.device)
-    _run("core", "ti_moe_combine_norm_add", x32.data_ptr(), _ptr(copy), down.data_ptr(), _ptr(shared_out),
+    _run("latent", "ti_moe_combine_norm_add", x32.data_ptr(), _ptr(copy), down.data_ptr(), _ptr(shared_out),
          routing.slot_of.data_ptr(), routing.weight.data_ptr(), norm_weight.data_ptr(), t, size,
          routing.chosen.shape[1], float(eps), 0 if copy is None else _dtype_code(copy), _stream())
     return x32, (x32 if copy is None else copy)
+
+
+# ---------------------------------------------------------------------- several residual streams
+def streams_embed(token_ids: torch.Tensor, table: torch.Tensor, streams: int) -> torch.Tensor:
+    """float32 [streams, T, width]: every stream starts as the rows ``table[token_ids]``."""
+    _check(token_ids, "token_ids", torch.int32, 1)
+    _check(table, "table", None, 2)
+    t, width = token_ids.shape[0], table.shape[1]
+    out = torch.empty((streams, t, width), dtype=torch.float32, device=table.device)
+    _run("hybrid", "ti_streams_embed", out.data_ptr(), table.data_ptr(), token_ids.data_ptr(), t, width, table.shape[0],
+         streams, _dtype_code(table), _stream())
+    return out
+
+
+class StreamUpdate:
+    """What a sublayer leaves for the streams, applied by the next ``streams_step``:
+    X[t] <- sum_s mix[s, t] X[s] + out[t] * y (``mix`` float32 [S, S] indexed [from, to], ``out`` float32 [S])."""
+
+    def __init__(self, y: torch.Tensor, mix: torch.Tensor, out: torch.Tensor):
+        self.y, self.mix, self.out = y, mix, out
+
+
+def streams_step(x: torch.Tensor, pending: Optional[StreamUpdate], read_in: Optional[torch.Tensor],
+                 norm_weight: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype,
+                 rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """One kernel between two sublayers of a model whose residual is several float32 streams ``x`` [S, T, W]:
+    applies ``pending`` in place (if any), then returns h = norm_weight * u * rsqrt(mean(u^2) + eps) in ``out_dtype``
+    with u = sum_s read_in[s] x[s] (if ``read_in`` is given; else None). ``rows`` int32 [N]: only these tokens are
+    worked on (h then has N rows): for the rows whose logits are wanted, at the very end."""
+    _check(x, "x", torch.float32, 3)
+    s, t, width = x.shape
+    y = None
+    if pending is not None:
+        y = _check(pending.y, "y", None, 2)
+        _check(pending.mix, "mix", torch.float32, 2)
+        _check(pending.out, "out", torch.float32, 1)
+        if tuple(y.shape) != (t, width) or tuple(pending.mix.shape) != (s, s) or pending.out.shape[0] != s:
+            raise KernelError("streams_step: the update does not fit the streams")
+    h = None
+    n = t if rows is None else _check(rows, "rows", torch.int32, 1).shape[0]
+    if read_in is not None:
+        _check(read_in, "read_in", torch.float32, 1)
+        _check(norm_weight, "norm_weight", torch.float32, 1)
+        if read_in.shape[0] != s or norm_weight.shape[0] != width:
+            raise KernelError("streams_step: the read coefficients or the norm do not fit the streams")
+        h = torch.empty((n, width), dtype=out_dtype, device=x.device)
+    _run("hybrid", "ti_streams_step", x.data_ptr(), _ptr(y), _ptr(pending.mix) if pending else None,
+         _ptr(pending.out) if pending else None, _ptr(read_in), _ptr(norm_weight), float(eps), _ptr(h), _ptr(rows), n, t,
+         width, s, _dtype_code(y) if y is not None else 0, _dtype_code(h) if h is not None else 0, _stream())
+    return h
+
+
+def gelu(x: torch.Tensor, tanh: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """0.5 z (1 + erf(z / sqrt 2)), or the tanh form; float32 arithmetic, one rounding. ``out`` may be ``x``."""
+    _check(x, "x")
+    if out is None:
+        out = torch.empty_like(x)
+    _run("hybrid", "ti_gelu", out.data_ptr(), x.data_ptr(), x.numel(), int(tanh), _dtype_code(x), _stream())
+    return out
+
+
+def scale_(x: torch.Tensor, factor: float) -> torch.Tensor:
+    """x *= factor in place (float32)."""
+    _check(x, "x", torch.float32)
+    if factor != 1.0:
+        _run("hybrid", "ti_scale", x.data_ptr(), x.numel(), float(factor), _stream())
+    return x
+
+
+# ---------------------------------------------------------------------- short convolutions, attention over [k | v] rows
+def _slot_stride(state: torch.Tensor, inner: int, name: str) -> int:
+    """``state`` float32 [slots, ...]: a slice of the per-request state whose slots lie stride(0) floats apart
+    and whose ``inner`` floats of a slot are contiguous."""
+    if not isinstance(state, torch.Tensor) or not state.is_cuda or state.dtype != torch.float32:
+        raise KernelError(f"{name} must be a float32 CUDA tensor")
+    if state[0].numel() != inner or not state[0].is_contiguous():
+        raise KernelError(f"{name}: a slot must hold {inner} contiguous floats, got shape {tuple(state.shape)}")
+    return state.stride(0)
+
+
+def short_conv(x: torch.Tensor, *, offset: int, width: int, history: torch.Tensor, weight: torch.Tensor,
+               bias: Optional[torch.Tensor], silu: bool, token_seq: torch.Tensor, cu_seqlens: torch.Tensor,
+               state_slots: torch.Tensor) -> torch.Tensor:
+    """Causal per-channel convolution over time of columns [offset, offset + width) of ``x`` [T, row], ``weight``
+    float32 [width, taps] (last column: the current token), then + bias and silu if asked. Inputs of earlier steps
+    come from ``history`` float32 [slots, taps - 1, width] (oldest first), which ``conv_state_update`` keeps."""
+    _check(x, "x", None, 2)
+    _check(weight, "weight", torch.float32, 2)
+    taps = weight.shape[1]
+    if weight.shape[0] != width or offset + width > x.shape[1]:
+        raise KernelError("short_conv: shapes do not match")
+    stride = _slot_stride(history, (taps - 1) * width, "history") if taps > 1 else 0
+    if bias is not None:
+        _check(bias, "bias", torch.float32, 1)
+    out = torch.empty((x.shape[0], width), dtype=x.dtype, device=x.device)
+    _run("hybrid", "ti_short_conv", out.data_ptr(), x.data_ptr(), x.shape[1], offset, history.data_ptr() if taps > 1 else None,
+         stride, weight.data_ptr(), _ptr(bias), token_seq.data_ptr(), cu_seqlens.data_ptr(), state_slots.data_ptr(),
+         x.shape[0], width, taps, int(silu), _dtype_code(x), _stream())
+    return out
+
+
+def conv_state_update(history: torch.Tensor, x: torch.Tensor, *, offset: int, width: int, taps: int,
+                      cu_seqlens: torch.Tensor, state_slots: torch.Tensor, num_seqs: int) -> None:
+    """The last taps - 1 rows of every request's columns [offset, offset + width) of ``x`` become its ``history``
+    (rows of a step shorter than that push the old ones up). Runs after the kernels that read the history."""
+    if taps <= 1:
+        return
+    _check(x, "x", None, 2)
+    stride = _slot_stride(history, (taps - 1) * width, "history")
+    _run("hybrid", "ti_conv_state_update", history.data_ptr(), stride, x.data_ptr(), x.shape[1], offset,
+         cu_seqlens.data_ptr(), state_slots.data_ptr(), num_seqs, width, taps, _dtype_code(x), _stream())
+
+
+def conv_qkv_append(qkv: torch.Tensor, *, num_heads: int, num_kv_heads: int, head_dim: int, v_dim: int,
+                    conv_weight: Optional[torch.Tensor], history: Optional[torch.Tensor],
+                    temperature: Optional[tuple], positions: torch.Tensor, token_seq: torch.Tensor,
+                    cu_seqlens: torch.Tensor, state_slots: torch.Tensor, cache: Optional[torch.Tensor],
+                    block_table: torch.Tensor, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``qkv`` [T, Hq d + Hkv (d + dv)] packed [q | k | v]: a short causal convolution per channel
+    (``conv_weight`` float32 [channels, taps] with ``history`` float32 [slots, taps - 1, channels]; None: none),
+    then q times its position's temperature 1 + coef * ln(floor((p + 1) / every) + 1) (``temperature`` =
+    (coef, every) or None). Returns q [T, Hq, d]; k and v go to the token's row [k | v] of ``cache``
+    [1, pages, Hkv, page, d + dv]."""
+    _check(qkv, "qkv", None, 2)
+    t = qkv.shape[0]
+    width = num_heads * head_dim + num_kv_heads * (head_dim + v_dim)
+    if qkv.shape[1] != width:
+        raise KernelError("conv_qkv_append: the packed rows do not match the head sizes")
+    taps, stride = 1, 0
+    if conv_weight is not None:
+        _check(conv_weight, "conv_weight", torch.float32, 2)
+        taps = conv_weight.shape[1]
+        if conv_weight.shape[0] != width:
+            raise KernelError("conv_qkv_append: one row of taps per packed channel")
+        if taps > 1:
+            stride = _slot_stride(history, (taps - 1) * width, "history")
+    _check(positions, "positions", torch.int32, 1)
+    _check(block_table, "block_table", torch.int32, 2)
+    page_size = num_pages = 1
+    if cache is not None:
+        _check(cache, "cache", qkv.dtype, 5)
+        if cache.shape[0] != 1 or cache.shape[2] != num_kv_heads or cache.shape[4] != head_dim + v_dim:
+            raise KernelError(f"cache shape {tuple(cache.shape)} is not [1, pages, Hkv, page, d + dv]")
+        num_pages, page_size = cache.shape[1], cache.shape[3]
+    coef, every = (float(temperature[0]), int(temperature[1])) if temperature else (0.0, 0)
+    q = torch.empty((t, num_heads, head_dim), dtype=qkv.dtype, device=qkv.device)
+    _run("hybrid", "ti_conv_qkv_append", q.data_ptr(), _ptr(cache), qkv.data_ptr(), history.data_ptr() if taps > 1 else None,
+         stride, _ptr(conv_weight), taps, coef, every, positions.data_ptr(), token_seq.data_ptr(), cu_seqlens.data_ptr(),
+         state_slots.data_ptr(), block_table.data_ptr(), block_table.shape[1], t, num_heads, num_kv_heads, head_dim, v_dim,
+         page_size, num_pages, _ptr(status), _dtype_code(qkv), _stream())
+    return q
+
+
+def attention_rows(q: torch.Tensor, cache: torch.Tensor, *, v_dim: int, positions: torch.Tensor, token_seq: torch.Tensor,
+                   block_table: torch.Tensor, scale: float, sink: Optional[float] = None, window: Optional[int] = None,
+                   out_scale: float = 1.0, step=None, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention of q [T, Hq, d] over pages whose rows are [k (d) | v (dv)] (``cache``
+    [1, pages, Hkv, page, d + dv]). ``sink``: a logit whose exponential joins every softmax denominator without a
+    value (0.0: one is added to the sum of exp(score)). Returns [T, Hq * dv], multiplied by ``out_scale`` before
+    its rounding."""
+    _check(q, "q", None, 3)
+    _check(cache, "cache", q.dtype, 5)
+    _check(positions, "positions", torch.int32, 1)
+    _check(token_seq, "token_seq", torch.int32, 1)
+    _check(block_table, "block_table", torch.int32, 2)
+    t, hq, d = q.shape
+    _, num_pages, hkv, page_size, row = cache.shape
+    if cache.shape[0] != 1 or row != d + v_dim:
+        raise KernelError("attention_rows: the cache's rows are not [k | v] of these sizes")
+    out = torch.empty((t, hq * v_dim), dtype=q.dtype, device=q.device)
+    if t == 0:
+        return out
+    _run("hybrid", "ti_attention_rows", out.data_ptr(), q.data_ptr(), cache.data_ptr(), positions.data_ptr(),
+         token_seq.data_ptr(), block_table.data_ptr(), block_table.shape[1], t, hq, hkv, d, v_dim, page_size, num_pages,
+         float(scale), int(window or 0), int(sink is not None), float(sink or 0.0), float(out_scale), _ptr(status),
+         _dtype_code(q), _stream())
+    return out
+
+
+# ---------------------------------------------------------------------- linear attention with a matrix state
+class ScanGate:
+    """How the decay of a linear-attention state is made from ``values`` (float32 [T, cols], read from column
+    ``offset``). ``kind`` 'raw': the decay itself; 'sigmoid_power': sigmoid(v)^(1 / tau) per key channel;
+    'step_size': dt = softplus(v + dt_bias[h]), decay exp(-exp(a_log[h]) dt) per head, and the keys are
+    multiplied by dt. ``per_channel``: one value per (head, key channel) instead of one per head."""
+    KINDS = {"raw": 0, "sigmoid_power": 1, "step_size": 2}
+
+    def __init__(self, kind: str, values: torch.Tensor, *, per_channel: bool, offset: int = 0, tau: float = 1.0,
+                 a_log: Optional[torch.Tensor] = None, dt_bias: Optional[torch.Tensor] = None):
+        if kind not in self.KINDS:
+            raise KernelError(f"unknown gate {kind!r}; known: {sorted(self.KINDS)}")
+        self.kind, self.values, self.per_channel, self.offset = kind, values, per_channel, offset
+        self.tau, self.a_log, self.dt_bias = tau, a_log, dt_bias
+
+
+def linear_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: ScanGate, *, state: torch.Tensor, heads: int,
+                groups: int, key_dim: int, value_dim: int, q_offset: int = 0, k_offset: int = 0, v_offset: int = 0,
+                q_scale: float = 1.0, skip: Optional[torch.Tensor] = None, cu_seqlens: torch.Tensor,
+                state_slots: torch.Tensor, num_seqs: int) -> torch.Tensor:
+    """Per request and head, over the step's tokens in order: S <- diag(a) S + k v^T, o = S^T (q * q_scale)
+    (+ skip[h] * v), from and back into ``state`` float32 [slots, heads, value_dim, key_dim] (S transposed).
+    q and k: columns [offset, + groups * key_dim) of their tensors (head h reads group h // (heads / groups));
+    v: columns [offset, + heads * value_dim). Returns o float32 [T, heads * value_dim]."""
+    for name, ten in (("q", q), ("k", k), ("v", v)):
+        _check(ten, name, q.dtype, 2)
+    _check(gate.values, "gate", torch.float32, 2)
+    t = q.shape[0]
+    if k.shape[0] != t or v.shape[0] != t or gate.values.shape[0] != t:
+        raise KernelError("linear_scan: one row per token in q, k, v and the gate")
+    if (q_offset + groups * key_dim > q.shape[1] or k_offset + groups * key_dim > k.shape[1]
+            or v_offset + heads * value_dim > v.shape[1]
+            or gate.offset + heads * (key_dim if gate.per_channel else 1) > gate.values.shape[1]):
+        raise KernelError("linear_scan: the columns do not fit the rows")
+    stride = _slot_stride(state, heads * key_dim * value_dim, "state")
+    for name, ten in (("a_log", gate.a_log), ("dt_bias", gate.dt_bias), ("skip", skip)):
+        if ten is not None:
+            _check(ten, name, torch.float32, 1)
+            if ten.shape[0] != heads:
+                raise KernelError(f"linear_scan: {name} has one entry per head")
+    out = torch.empty((t, heads * value_dim), dtype=torch.float32, device=q.device)
+    if t == 0:
+        return out
+    _run("hybrid", "ti_linear_scan", out.data_ptr(), state.data_ptr(), stride, q.data_ptr(), q.shape[1], q_offset,
+         k.data_ptr(), k.shape[1], k_offset, v.data_ptr(), v.shape[1], v_offset, gate.values.data_ptr(),
+         gate.values.shape[1], gate.offset, ScanGate.KINDS[gate.kind], int(gate.per_channel), float(gate.tau),
+         _ptr(gate.a_log), _ptr(gate.dt_bias), _ptr(skip), float(q_scale), cu_seqlens.data_ptr(), state_slots.data_ptr(),
+         num_seqs, heads, groups, key_dim, value_dim, _dtype_code(q), _stream())
+    return out
+
+
+def gated_group_norm(y: torch.Tensor, gate: Optional[torch.Tensor], weight: torch.Tensor, *, group: int, eps: float,
+                     gate_first: bool, out_dtype: torch.dtype, gate_offset: int = 0, out_scale: float = 1.0) -> torch.Tensor:
+    """Every ``group`` neighbouring features of y (float32 [T, C]) divided by their root mean square, times
+    ``weight`` (float32, repeated along the row if shorter) and ``out_scale``; silu of columns [gate_offset, + C) of
+    ``gate`` multiplies y before the norm (``gate_first``) or the result after it. One rounding to ``out_dtype``."""
+    _check(y, "y", torch.float32, 2)
+    _check(weight, "weight", torch.float32, 1)
+    t, c = y.shape
+    if c % group or c % weight.shape[0]:
+        raise KernelError("gated_group_norm: the row does not split into these groups or weights")
+    if gate is not None:
+        _check(gate, "gate", out_dtype, 2)
+        if gate.shape[0] != t or gate_offset + c > gate.shape[1]:
+            raise KernelError("gated_group_norm: the gate does not fit")
+    out = torch.empty((t, c), dtype=out_dtype, device=y.device)
+    _run("hybrid", "ti_gated_group_norm", out.data_ptr(), y.data_ptr(), _ptr(gate), gate.shape[1] if gate is not None else 0,
+         gate_offset, weight.data_ptr(), weight.shape[0], t, c, group, float(eps), int(gate_first), float(out_scale),
+         _dtype_code(out), _stream())
+    return out
 
 
 # ---------------------------------------------------------------------- sampling

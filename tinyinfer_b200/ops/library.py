@@ -4,7 +4,8 @@ Each library is a plain shared object with ``extern "C"`` launchers, compiled by
 first use and kept in ``tinyinfer_b200/csrc/_build`` (or, if the checkout is read-only, in a
 per-user folder under the system's temporary directory). The file name carries a hash of the
 sources and flags, so an edited kernel is rebuilt and a stale object is never loaded. A library
-is only built when something asks for it: a 32-bit run never compiles the tensor-core kernels.
+is only built when something asks for it: a 32-bit run never compiles the tensor-core kernels, and a model
+builds only the libraries its own parts call.
 
 There is no fallback: if ``nvcc`` or the build fails, loading raises.
 """
@@ -31,12 +32,18 @@ COMMON_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcomp
                 "-fvisibility=hidden"]
 
 LIBRARIES: Dict[str, dict] = {
-    # every dtype, every shape: the 32-bit path and the general bfloat16 path
+    # every dtype, every shape: the 32-bit path and the general bfloat16 path of the plain decoder, and sampling
     "core": dict(sources=["runtime.cu", "elementwise.cu", "rope_append.cu",
-                          "attention_generic.cu", "gemm_simt.cu", "sampling.cu", "stream.cu",
-                          "gemm_batched.cu", "latent_attention.cu", "latent_attention_mma.cu", "recurrent.cu",
-                          "experts.cu"],
-                 headers=["common.cuh", "mma_tile.cuh"], link=[]),
+                          "attention_generic.cu", "gemm_simt.cu", "sampling.cu"],
+                 headers=["common.cuh"], link=[]),
+    # parts of designs with a cached latent, gated recurrences and routed experts around a float32 stream
+    "latent": dict(sources=["runtime.cu", "stream.cu", "gemm_batched.cu", "latent_attention.cu",
+                            "latent_attention_mma.cu", "recurrent.cu", "experts.cu"],
+                   headers=["common.cuh", "mma_tile.cuh"], link=[]),
+    # parts of designs with several residual streams, short convolutions, attention over [key | value] rows and
+    # linear attention with a matrix state
+    "hybrid": dict(sources=["runtime.cu", "hyper_streams.cu", "conv_attention.cu", "linear_scan.cu"],
+                   headers=["common.cuh"], link=[]),
     # bfloat16 tensor-core kernels (tcgen05 + TMA); only a bfloat16 model loads it
     "sm100": dict(sources=["runtime.cu", "sm100_host.cu", "gemm_tcgen05.cu", "attention_mma.cu",
                            "attention_prefill_tcgen05.cu", "attention_prefill_pair_tcgen05.cu", "gemm_pair_tcgen05.cu",

@@ -21,10 +21,12 @@ class TensorSpec:
     """A tensor a part wants from the checkpoint.
     role 'matrix': kept in the compute dtype (bfloat16 or float32);
     role 'vector32': kept in float32 whatever the compute dtype (norm weights, biases of
-    32-bit parts); role 'int': kept as int32."""
+    32-bit parts); role 'int': kept as int32. A size of -1 is one that only the checkpoint gives (the
+    loader accepts any; the random-weights mode cannot draw such a tensor)."""
     shape: Tuple[int, ...]
     role: str = "matrix"
-    init: str = "normal"          # random-weights mode: 'normal' N(0, std) or 'ones_noise' 1 + N(0, 0.1)
+    init: str = "normal"          # random-weights mode: 'normal' N(0, std), 'ones_noise' 1 + N(0, 0.1) or
+                                  # 'eye_noise' (a square matrix) identity + N(0, 0.1)
 
 
 @dataclass(frozen=True)
@@ -46,6 +48,21 @@ class StateNeed:
     dtype: torch.dtype = torch.float32
 
 
+def state_slices(state: torch.Tensor, shapes):
+    """Cuts a per-request state float32 [slots, n] into consecutive pieces of the given shapes:
+    views [slots, *shape] whose slots lie as far apart as the whole state's."""
+    out, at = [], 0
+    for shape in shapes:
+        n = 1
+        for d in shape:
+            n *= d
+        out.append(state[:, at:at + n].unflatten(1, tuple(shape)))
+        at += n
+    if at > state.shape[1]:
+        raise ValueError(f"a state of {state.shape[1]} floats a slot does not hold {at}")
+    return out
+
+
 class Part:
     def __init__(self, spec, dtype: torch.dtype, device):
         self.spec = spec
@@ -58,6 +75,11 @@ class Part:
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         """Receives exactly the tensors named by ``tensors()``, on the device, role applied."""
+
+    def parts(self):
+        """The parts this part is made of, if any (a mixer of several mixers): whoever lets go of a model's
+        tensors walks through them."""
+        return []
 
 
 class Norm(Part):
@@ -111,6 +133,13 @@ class Mixer(Part):
         from .. import ops
         return ops.add(residual, self.forward(x, step, cache))
 
+    def forward_scaled(self, x, scale: float, residual, step, cache) -> torch.Tensor:
+        """scale * forward(x) (+ residual): what a mixer that runs beside others contributes to their sum.
+        Parts that can fold the factor into a kernel they launch anyway override this."""
+        if scale != 1.0:
+            raise NotImplementedError(f"{type(self).__name__} cannot scale its output; it cannot stand in a sum of mixers")
+        return self.forward(x, step, cache) if residual is None else self.forward_residual(x, residual, step, cache)
+
     def forward_prenorm(self, x, norm: "Norm", link, next_norm: Optional["Norm"], step, cache):
         """x + forward(norm(x)) for ``x`` BEFORE its norm. ``link``: None, or what the part that made x
         left for this norm (an ``ops.NormLink``); ``next_norm``: the norm the result will pass through
@@ -145,6 +174,13 @@ class Block:
         self.feed_forward = feed_forward
         self.mixer_norm = mixer_norm
         self.feed_forward_norm = feed_forward_norm
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        """Tensors the arrangement itself owns, named from the layer's prefix (most have none)."""
+        return {}
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        pass
 
     def forward(self, x, step, cache):
         raise NotImplementedError

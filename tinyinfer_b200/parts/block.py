@@ -44,5 +44,62 @@ class OutputNormBlock(Block):
         return (x32, copy), None
 
 
+class MultiStreamBlock(Block):
+    """The residual is ``streams`` float32 copies X [S, T, W] (hyper-connections). Sublayer q (1: the mixer,
+    2: the feed-forward) reads u = sum_s in_q[s] X[s] through its norm and leaves
+    X[t] <- sum_s mix_q[s, t] X[s] + out_q[t] * y for all streams at once. What travels between blocks is the pair
+    (X, update still to be applied): one kernel applies the update a sublayer left and makes the next sublayer's
+    input, so a sublayer costs one kernel for all of its residual work. With ``learned_mixing`` the block owns
+    ``hc1.{in,out,mix}`` (and ``hc2.*`` if it has a feed-forward); without, all coefficients are 1, which with one
+    stream is the pre-norm residual kept in float32. A block may have no feed-forward."""
+
+    def _coefficients(self):
+        return [f"hc{q}" for q in ((1, 2) if self.feed_forward is not None else (1,))]
+
+    def tensors(self):
+        from .base import TensorSpec
+        if not self.spec.learned_mixing:
+            return {}
+        n = self.spec.streams
+        out = {}
+        for name in self._coefficients():
+            out[f"{name}.in"] = TensorSpec((n,), role="vector32", init="ones_noise")
+            out[f"{name}.out"] = TensorSpec((n,), role="vector32", init="ones_noise")
+            out[f"{name}.mix"] = TensorSpec((n, n), role="vector32", init="eye_noise")
+        return out
+
+    def load(self, tensors):
+        self.coefficients = {name: tensors[name].contiguous() for name in self.tensors()}
+
+    def _coef(self, name: str, device):
+        table = getattr(self, "coefficients", None)
+        if table is None:
+            table = self.coefficients = {}
+        if name not in table:              # not learned: all ones
+            import torch
+            n = self.spec.streams
+            table[name] = torch.ones((n, n) if name.endswith(".mix") else (n,), dtype=torch.float32, device=device)
+        return table[name]
+
+    def forward(self, x, step, cache):
+        return self.forward_linked(x, None, None, step, cache)[0]
+
+    def forward_linked(self, x, link, next_norm, step, cache):
+        from .. import ops
+        streams, pending = x
+        dev, dtype = streams.device, self.mixer.dtype
+        sublayers = [("hc1", self.mixer_norm, lambda h: self.mixer.forward(h, step, cache))]
+        if self.feed_forward is not None:
+            sublayers.append(("hc2", self.feed_forward_norm, lambda h: self.feed_forward.forward(h, step)))
+        for name, norm, run in sublayers:
+            rms = norm.as_rms()
+            if rms is None:
+                raise ValueError("the multi-stream arrangement needs RMSNorms")
+            h = ops.streams_step(streams, pending, self._coef(f"{name}.in", dev), rms[0], rms[1], dtype)
+            pending = ops.StreamUpdate(run(h), self._coef(f"{name}.mix", dev), self._coef(f"{name}.out", dev))
+        return (streams, pending), None
+
+
 register_block("pre_norm", PreNormBlock)
+register_block("multi_stream", MultiStreamBlock)
 register_block("output_norm", OutputNormBlock)

@@ -51,4 +51,41 @@ class GatedMLP(FeedForward):
         return ops.linear(hidden, self.w_down, residual=x, next_norm_weight=after[0])
 
 
+class DenseMLP(FeedForward):
+    """Dense feed-forward without a gate: down(act(up h + b_up)) + b_down, act the exact (erf) gelu or its tanh
+    form, computed in float32 on the stored product and rounded once."""
+    graph_safe = True
+
+    def __init__(self, spec, dtype, device):
+        super().__init__(spec, dtype, device)
+        if spec.activation not in ("gelu", "gelu_tanh"):
+            raise ValueError(f"activation {spec.activation!r} is not supported (gelu, gelu_tanh)")
+        self.w_up = self.b_up = self.w_down = self.b_down = None
+
+    def tensors(self):
+        s = self.spec
+        t = {"up": TensorSpec((s.intermediate_size, s.hidden_size)),
+             "down": TensorSpec((s.hidden_size, s.intermediate_size))}
+        if s.bias:
+            t["up.b"] = TensorSpec((s.intermediate_size,), role="vector32")
+            t["down.b"] = TensorSpec((s.hidden_size,), role="vector32")
+        return t
+
+    def load(self, tensors):
+        self.w_up, self.w_down = tensors["up"].contiguous(), tensors["down"].contiguous()
+        if self.spec.bias:
+            self.b_up, self.b_down = tensors["up.b"], tensors["down.b"]
+
+    def _hidden(self, x):
+        up = ops.linear(x, self.w_up, bias=self.b_up)
+        return ops.gelu(up, tanh=self.spec.activation == "gelu_tanh", out=up)
+
+    def forward(self, x, step=None):
+        return ops.linear(self._hidden(x), self.w_down, bias=self.b_down)
+
+    def forward_residual(self, x, residual, step=None):
+        return ops.linear(self._hidden(x), self.w_down, bias=self.b_down, residual=residual)
+
+
 register_feed_forward("gated_mlp", GatedMLP)
+register_feed_forward("dense_mlp", DenseMLP)

@@ -81,8 +81,11 @@ def load_weights(model, folder) -> LoadReport:
     index = checkpoint_index(folder)
     missing = [n for n in expected if n not in index]
     unexpected = sorted(n for n in index if n not in expected and n not in ignored)
+    def fits(got, want):          # a size of -1 is one that only the checkpoint gives
+        return len(got) == len(want) and all(w == -1 or g == w for g, w in zip(got, want))
+
     wrong = [(n, index[n][1], expected[n].shape) for n in expected
-             if n in index and tuple(index[n][1]) != tuple(expected[n].shape)]
+             if n in index and not fits(tuple(index[n][1]), tuple(expected[n].shape))]
     if missing or unexpected or wrong:
         raise WeightError(missing, unexpected, wrong, where=str(folder))
 

@@ -20,11 +20,16 @@ from .loader import apply_role
 
 
 def _draw(ts, generator, std: float, device="cpu") -> torch.Tensor:
+    if any(d < 0 for d in ts.shape):
+        raise ValueError(f"a tensor of shape {ts.shape} has a size that only a checkpoint gives: name it in the "
+                         "configuration to draw random weights")
     if ts.role == "int":
         return torch.zeros(ts.shape, dtype=torch.int32, device=device)
     t = torch.randn(ts.shape, generator=generator, dtype=torch.float32, device=device)
     if ts.init == "ones_noise":
         return 1.0 + 0.1 * t
+    if ts.init == "eye_noise":
+        return torch.eye(ts.shape[0], ts.shape[1], dtype=torch.float32, device=device) + 0.1 * t
     return t * std
 
 
