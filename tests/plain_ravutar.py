@@ -55,15 +55,15 @@ def query_temperature(positions: torch.Tensor, coef: float, every: int, dtype) -
     return 1.0 + coef * torch.log(steps + 1.0)
 
 
-def sink_attention(h: torch.Tensor, w: Dict[str, torch.Tensor], m: dict) -> torch.Tensor:
+def sink_attention(h: torch.Tensor, w: Dict[str, torch.Tensor], m: dict, sink: bool = True) -> torch.Tensor:
     """Grouped-query causal softmax attention without a rotation: biased projections, a short convolution on
     q, k and v, a query temperature that grows with the position, and a softmax whose denominator holds one
-    more term exp(0) that has no value."""
+    more term exp(0) that has no value (``sink`` False leaves that term out: what a test compares with)."""
     T = h.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q = short_conv(h @ w["q"].T + w["q.b"], w["q.conv"])
-    k = short_conv(h @ w["k"].T + w["k.b"], w["k.conv"])
-    v = short_conv(h @ w["v"].T + w["v.b"], w["v.conv"])
+    q, k, v = (h @ w[n].T + w[n + ".b"] for n in ("q", "k", "v"))
+    if "q.conv" in w:
+        q, k, v = (short_conv(u, w[n + ".conv"]) for u, n in ((q, "q"), (k, "k"), (v, "v")))
     pos = torch.arange(T)
     qt = m.get("q_temp")
     if qt:
@@ -77,7 +77,7 @@ def sink_attention(h: torch.Tensor, w: Dict[str, torch.Tensor], m: dict) -> torc
         s = s.masked_fill(pos[None, :] > pos[:, None], float("-inf"))
         top = torch.clamp(s.max(dim=-1, keepdim=True).values, min=0.0)
         e = torch.exp(s - top)
-        p = e / (torch.exp(-top) + e.sum(dim=-1, keepdim=True))
+        p = e / ((torch.exp(-top) if sink else 0.0) + e.sum(dim=-1, keepdim=True))
         out[:, head] = p @ v[:, g]
     return out.reshape(T, H * dv) @ w["o"].T + w["o.b"]
 
@@ -103,7 +103,7 @@ def gated_linear_attention(h: torch.Tensor, w: Dict[str, torch.Tensor], m: dict,
 
 
 def parallel_mixer(h: torch.Tensor, w: Dict[str, torch.Tensor], m: dict, eps: float) -> torch.Tensor:
-    left = sink_attention(h, _sub(w, "left."), m["left"])
+    left = sink_attention(h, _sub(w, "left."), m["left"], sink=not m.get("test_without_sink"))
     right = gated_linear_attention(h, _sub(w, "right."), m["right"], eps)
     return float(m["left_scale"]) * left + float(m["right_scale"]) * right
 

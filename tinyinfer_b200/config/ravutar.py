@@ -134,7 +134,7 @@ class RavutarConfig:
                 attention = ConvAttentionSpec(
                     hidden_size=width, num_heads=int(left["heads"]), num_kv_heads=int(left["kv_heads"]),
                     head_dim=int(left["dim"]), v_dim=int(left["vdim"]), scale=float(left["scale"]),
-                    conv_taps=int(left.get("conv", 1)),
+                    conv_taps=int(left.get("conv", 0)),
                     query_temperature=(float(qt["coef"]), int(qt["every"])) if qt else None, sink=SINK_LOGIT, bias=True)
                 linear = GatedLinearAttentionSpec(
                     hidden_size=width, num_heads=int(right["heads"]), key_dim=int(right["dim"]),

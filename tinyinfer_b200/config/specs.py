@@ -118,7 +118,8 @@ class ExpertsSpec:
 @dataclass(frozen=True)
 class ConvAttentionSpec:
     """Grouped-query softmax attention without a rotation, whose q, k and v pass a short causal convolution over
-    time (``conv_taps`` taps per channel; 1: none) right after their projections. Keys have ``head_dim`` features,
+    time (``conv_taps`` taps per channel; one tap is a weight per channel; 0: no convolution) right after their
+    projections. Keys have ``head_dim`` features,
     values ``v_dim``. ``query_temperature`` (coef, every): the query at position p is multiplied by
     1 + coef * ln(floor((p + 1) / every) + 1). ``sink``: a logit whose exponential joins the softmax denominator
     without a value (0.0 adds one to the sum of exp(score)); None: the ordinary softmax."""
@@ -128,7 +129,7 @@ class ConvAttentionSpec:
     head_dim: int
     v_dim: int
     scale: float
-    conv_taps: int = 1
+    conv_taps: int = 0
     query_temperature: Optional[Tuple[float, int]] = None
     sink: Optional[float] = None
     bias: bool = True

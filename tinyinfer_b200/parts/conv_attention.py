@@ -21,8 +21,8 @@ class ConvAttention(Mixer):
         super().__init__(spec, dtype, device)
         if spec.num_heads % spec.num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
-        if spec.conv_taps < 1:
-            raise ValueError("conv_taps must be at least 1")
+        if spec.conv_taps < 0:
+            raise ValueError("conv_taps must not be negative")
         self.w_qkv = self.b_qkv = self.conv_w = self.w_o = self.b_o = None
 
     # packed channels: [q | k | v]
@@ -47,7 +47,7 @@ class ConvAttention(Mixer):
         if s.bias:
             t.update({"q.b": TensorSpec((nq,), role="vector32"), "k.b": TensorSpec((nk,), role="vector32"),
                       "v.b": TensorSpec((nv,), role="vector32"), "o.b": TensorSpec((s.hidden_size,), role="vector32")})
-        if s.conv_taps > 1:
+        if s.conv_taps >= 1:
             t.update({"q.conv": TensorSpec((nq, s.conv_taps), role="vector32", init="ones_noise"),
                       "k.conv": TensorSpec((nk, s.conv_taps), role="vector32", init="ones_noise"),
                       "v.conv": TensorSpec((nv, s.conv_taps), role="vector32", init="ones_noise")})
@@ -60,7 +60,7 @@ class ConvAttention(Mixer):
         if s.bias:
             self.b_qkv = torch.cat([tensors["q.b"], tensors["k.b"], tensors["v.b"]]).contiguous()
             self.b_o = tensors["o.b"]
-        if s.conv_taps > 1:
+        if s.conv_taps >= 1:
             self.conv_w = torch.cat([tensors["q.conv"], tensors["k.conv"], tensors["v.conv"]], dim=0).contiguous()
 
     def _attend(self, x, step, cache, out_scale=1.0):
