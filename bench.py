@@ -20,7 +20,9 @@ CPU implementation of the tests, in seconds, beside the engine's time for the sa
 
 ``--design gulisun`` leaves the headline workload alone and instead prints one JSON line with the prefill and
 decode throughput of the Gulisun design (latent attention, gated recurrences, routed experts) at two sizes with
-the layer sizes of real models, each beside the Qwen3 preset of the same width and number of layers.
+the layer sizes of real models, each beside the Qwen3 preset of the same width and number of layers;
+``--design ravutar`` does the same for the Ravutar design (attention with short convolutions and a sink beside gated
+linear attention, state-space layers, several residual streams).
 
 ``--impl reference`` runs the unmodified reference project from ``baseline/_ref`` through its own
 public API (``tinyinfer.LLM(Config(...))``, ``add_request``, ``step``) on a model folder of the same
@@ -540,6 +542,42 @@ def gulisun_numbers(cfg, batch, context):
     return dict(macs=macs, attn_per_key=attn_per_key, head=head, step_bytes=step_bytes)
 
 
+def ravutar_numbers(cfg, batch, context):
+    """As ``gulisun_numbers`` for the Ravutar design: matrix elements a token multiplies, attention flops per key,
+    flops a token spends in the matrix-state recurrences, and the bytes a decode step must move (weights, the head,
+    the cached keys and values of every attention branch, every request's matrix states read and written)."""
+    w, macs, attn_per_key, scan_flops, cache_per_token, state_bytes = cfg.width, 0, 0.0, 0.0, 0, 0
+    for i in cfg.run_order():
+        layer = cfg.layers[i]
+        m, f = layer["mixer"], layer.get("mlp")
+        if layer["type"] == "parallel":
+            a, b = m["left"], m["right"]
+            h, g, d, v = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+            macs += w * (h * d + g * (d + v)) + w * h * v
+            attn_per_key += 2.0 * h * (d + v)
+            cache_per_token += g * (d + v) * 2
+            rh, rk, rv, rank = b["heads"], b["dim"], b["vdim"], b.get("gate_rank", 16)
+            macs += w * (2 * rh * rk + 2 * rh * rv) + rank * w + rank * rh * rk + w * rh * rv
+            scan_flops += 4.0 * rh * rk * rv
+            state_bytes += rh * rk * rv * 4 * 2
+        else:
+            inner, gn = m["heads"] * m["vdim"], m["groups"] * m["state"]
+            macs += w * (2 * inner + 2 * gn + m["heads"]) + w * inner
+            scan_flops += 4.0 * m["heads"] * m["state"] * m["vdim"]
+            state_bytes += m["heads"] * m["state"] * m["vdim"] * 4 * 2
+        if f is not None:
+            macs += 2 * f["ff"] * w
+    head = cfg.vocab * w
+    step_bytes = macs * 2 + head * 2 + batch * context * cache_per_token + batch * state_bytes
+    return dict(macs=macs, attn_per_key=attn_per_key, head=head, step_bytes=step_bytes, scan_flops=scan_flops)
+
+
+DESIGNS = {      # design -> (what its numbers are made with, [(its preset, the Qwen3 preset of the same width)])
+    "gulisun": (gulisun_numbers, (("gulisun-1b", "0.6b"), ("gulisun-2b", "1.7b"))),
+    "ravutar": (ravutar_numbers, (("ravutar-1b", "0.6b"), ("ravutar-2b", "1.7b"))),
+}
+
+
 def measure_design(cfg, peaks, flops_of_prefill, bytes_of_step, batch, context, steps, warmup, prefill_tokens):
     """Prefill of one prompt and decode at ``batch`` requests of ``context`` tokens, device-timed, through the
     step function (the same measurement as the headline's)."""
@@ -593,20 +631,23 @@ def measure_design(cfg, peaks, flops_of_prefill, bytes_of_step, batch, context, 
 
 
 def design_comparison(args) -> int:
-    """``--design gulisun``: the design at two sizes beside the Qwen3 preset of the same width, both cut to the same
+    """``--design NAME``: the design at two sizes beside the Qwen3 preset of the same width, both cut to the same
     number of layers; one JSON line."""
     from tinyinfer_b200.config import preset_config
     peaks, peak_source = load_peaks()
     steps, warmup = args.steps, max(3, args.warmup)
     batch, context, prefill_tokens = args.batch, min(args.context, 2048), 2048
     sizes = {}
-    for ours, theirs in (("gulisun-1b", "0.6b"), ("gulisun-2b", "1.7b")):
+    design = args.design
+    numbers_of, pairs = DESIGNS[design]
+    for ours, theirs in pairs:
         g = preset_config(ours)
-        layers = len(g.layers)
-        numbers = gulisun_numbers(g, batch, context)
+        layers = len(g.run_order()) if hasattr(g, "run_order") else len(g.layers)
+        numbers = numbers_of(g, batch, context)
         t = prefill_tokens
-        flops = 2.0 * numbers["macs"] * t + numbers["attn_per_key"] * t * (t + 1) / 2.0 + 2.0 * numbers["head"]
-        row = {"layers": layers, "gulisun": measure_design(g, peaks, flops, numbers["step_bytes"], batch, context, steps,
+        flops = (2.0 * numbers["macs"] * t + numbers["attn_per_key"] * t * (t + 1) / 2.0 + 2.0 * numbers["head"]
+                 + numbers.get("scan_flops", 0.0) * t)
+        row = {"layers": layers, design: measure_design(g, peaks, flops, numbers["step_bytes"], batch, context, steps,
                                                            warmup, prefill_tokens)}
         q = preset_config(theirs, num_hidden_layers=layers)
         qn = model_numbers(q, layers)
@@ -614,10 +655,10 @@ def design_comparison(args) -> int:
                                       qn["weight_bytes"] + batch * context * qn["kv_bytes_per_token"], batch, context,
                                       steps, warmup, prefill_tokens)
         row["qwen3"]["preset"] = theirs
-        row["prefill_ratio"] = row["gulisun"]["prefill_tok_s"] / row["qwen3"]["prefill_tok_s"]
-        row["decode_ratio"] = row["gulisun"]["decode_tok_s"] / row["qwen3"]["decode_tok_s"]
+        row["prefill_ratio"] = row[design]["prefill_tok_s"] / row["qwen3"]["prefill_tok_s"]
+        row["decode_ratio"] = row[design]["decode_tok_s"] / row["qwen3"]["decode_tok_s"]
         sizes[ours] = row
-    print(json.dumps({"metric": "prefill and decode tok/s of the Gulisun design beside Qwen3 at equal width and depth",
+    print(json.dumps({"metric": f"prefill and decode tok/s of the {design.capitalize()} design beside Qwen3 at equal width and depth",
                       "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "bf16",
                       "data": "synthetic token ids, random-init weights", "peaks": peak_source, "sizes": sizes}))
     return 0
@@ -638,7 +679,7 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch")
     ap.add_argument("--skip-extras", action="store_true", help="leave out the 'configs' of the line")
     ap.add_argument("--extras", default="32b,mix,cpu", help="which of the other configurations to run")
-    ap.add_argument("--design", default="", choices=["", "gulisun"],
+    ap.add_argument("--design", default="", choices=["", "gulisun", "ravutar"],
                     help="instead of the headline: prefill and decode of this design beside Qwen3 at equal size")
     ap.add_argument("--ref-block-size", type=int, default=256, help="reference arm: its kvcache_block_size (its default)")
     ap.add_argument("--ref-step-tokens", type=int, default=32,

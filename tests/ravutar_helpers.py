@@ -69,6 +69,12 @@ ONE = config([parallel(left(3, 3, 8, 8, q_temp=(0.5, 4)), right(1, 40, 8), mlp=d
               mamba(3, 8, 8, 3, conv=2, norm_groups=1)], width=40, streams=1)
 
 
+# keys and values of one size (64): the cache of two planes and, in bfloat16, the tensor-core attention kernels
+SAME = config([parallel(left(4, 2, 64, 64, scale=0.2, conv=3, q_temp=(0.3, 16)), right(2, 32, 64, tau=9.0, gate_rank=8), mlp=dense(64)),
+               parallel(left(2, 2, 64, 64, scale=0.2, conv=None), right(2, 64, 32, tau=9.0, gate_rank=8))],
+              width=128, vocab=200, streams=2)
+
+
 def tensor_shapes(cfg: dict) -> Dict[str, tuple]:
     W = cfg["width"]
     shapes = {"embed": (cfg["vocab"], W), "head": (cfg["vocab"], W), "final.norm": (W,)}

@@ -85,10 +85,11 @@ def scan_plain(q, k, v, a, kscale, skip, S):
                                                      (4, 4, 64, 64, "step_size"), (2, 2, 300, 5, "raw")])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_linear_scan_against_plain(heads, groups, dk, dv, gate, dtype):
-    """Two requests of unequal length in two calls: the state goes through slots that lie inside a larger state."""
+    """Two requests of unequal length in two calls: the state goes through slots that lie inside a larger state.
+    The first call is long enough to be cut into stretches that run side by side (the short request's are partly empty)."""
     from tinyinfer_b200 import ops
     gen = torch.Generator().manual_seed(heads * dk + dv)
-    lens1, lens2 = [37, 5], [1, 22]
+    lens1, lens2 = [137, 5], [1, 22]
     per_channel = gate != "step_size"
     pad = 7                                              # other columns in front of q, k, v in their rows
     a_log, dt_bias, skip = torch.randn(heads, generator=gen) - 1, torch.randn(heads, generator=gen), torch.randn(heads, generator=gen)
@@ -107,7 +108,9 @@ def test_linear_scan_against_plain(heads, groups, dk, dv, gate, dtype):
         sg = ops.ScanGate(gate, g.cuda(), per_channel=per_channel, offset=3, tau=5.0, a_log=a_log.cuda(), dt_bias=dt_bias.cuda())
         got = ops.linear_scan(row.cuda(), row.cuda(), row.cuda(), sg, state=view, heads=heads, groups=groups, key_dim=dk,
                               value_dim=dv, q_offset=pad, k_offset=pad + groups * dk, v_offset=pad + 2 * groups * dk,
-                              q_scale=0.5, skip=skip.cuda(), cu_seqlens=cu.cuda(), state_slots=slots.cuda(), num_seqs=2).cpu()
+                              q_scale=0.5, skip=skip.cuda(), cu_seqlens=cu.cuda(), state_slots=slots.cuda(), num_seqs=2,
+                              max_q_len=max(lens)).cpu()
+        assert (ops.scan_stretches(max(lens), 2, heads, dk, dv) > 1) == (max(lens) > 100)
         r = row.double()
         per = heads // groups
         q = r[:, pad:pad + groups * dk].reshape(T, groups, dk).repeat_interleave(per, dim=1) * 0.5
@@ -157,6 +160,46 @@ def test_gelu_and_scale():
     tanh_form = 0.5 * x.double() * (1 + torch.tanh(0.7978845608028654 * (x.double() + 0.044715 * x.double() ** 3)))
     assert (ops.gelu(x.cuda(), tanh=True).cpu().double() - tanh_form).abs().max() < 1e-6
     assert torch.equal(ops.scale_(x.clone().cuda(), 0.25).cpu(), x * 0.25)
+
+
+SINK_SHAPES = [
+    # hq, hkv, d, page, window, [(context, q_len)], two query tiles a CTA?
+    (3, 3, 48, 5, None, [(17, 17), (31, 1)], False),                                    # the float32-arithmetic kernel
+    (8, 2, 64, 16, None, [(130, 130), (129, 1), (200, 2)], False),                      # one query tile a CTA; decoding
+    (8, 8, 128, 16, None, [(1500, 1), (1, 1), (256, 1), (257, 1), (1024, 1)], False),   # decoding, merged and not
+    (12, 3, 128, 64, None, [(450, 61), (63, 63), (2, 2), (1100, 17)], False),
+    (8, 2, 128, 64, None, [(1300, 897), (700, 513), (640, 384), (1, 1)], True),         # two query tiles a CTA
+    (4, 2, 64, 32, 200, [(1500, 1000), (420, 385)], True),
+    (2, 1, 128, 64, None, [(4000, 120)], False),                                        # the keys shared out over CTAs
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("sink", [0.0, 2.5, -30.0])
+@pytest.mark.parametrize("hq,hkv,d,page,window,work,pairs", SINK_SHAPES)
+def test_paged_attention_with_a_sink(monkeypatch, dtype, sink, hq, hkv, d, page, window, work, pairs):
+    """The softmax denominator's extra term and the output factor in every attention kernel of the plain decoder."""
+    import test_kernels_gpu as tk
+    import torch_ops as ref
+    from tinyinfer_b200 import ops
+    if dtype == torch.float32 and sink != 0.0:
+        pytest.skip("one sink in float32")
+    monkeypatch.setattr(ops, "PAIR_MIN_CTAS", 0 if pairs else 1 << 30)
+    lens = [c for c, _ in work]
+    bt, kv = tk.paged_setup(dtype, lens, hq, hkv, d, page, seed=1)
+    tk.fill_cache(kv, bt, lens, hkv, d, page, dtype)
+    pos = torch.tensor([p for c, n in work for p in range(c - n, c)], dtype=torch.int32, device="cuda")
+    seq = torch.tensor([i for i, (c, n) in enumerate(work) for _ in range(n)], dtype=torch.int32, device="cuda")
+    q = tk.rnd(pos.shape[0], hq, d, dtype=dtype, seed=7, std=2.0)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    args = dict(positions=pos, token_seq=seq, block_table=bt, scale=d ** -0.5, window=window, sink=sink, out_scale=0.7)
+    out = ops.paged_attention(q, kv, status=status, **args)
+    assert int(status.item()) == 0 and torch.isfinite(out.float()).all()
+    want = ref.paged_attention(q, kv, **args)
+    tk.close(out, want, dtype)
+    if sink > -10 and max(lens) <= 1500 and window is None:          # few enough keys that the term carries weight
+        without = ref.paged_attention(q, kv, **dict(args, sink=None))
+        assert (without.float() - want.float()).abs().max() > 0.05
 
 
 # ------------------------------------------------------------------ each mechanism alone
@@ -220,7 +263,7 @@ def traces_for(requests, max_live=4):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name,page", [("MIX", 8), ("WIDE", 16), ("ONE", 4)])
+@pytest.mark.parametrize("name,page", [("MIX", 8), ("WIDE", 16), ("ONE", 4), ("SAME", 16)])
 def test_every_cut_matches_plain(tmp_path, name, page, dtype):
     cfg = getattr(rh, name)
     folder = rh.write_folder(tmp_path / name, cfg, seed=3, dtype=dtype)

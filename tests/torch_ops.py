@@ -102,7 +102,8 @@ def qk_norm_rope_append(qkv, *, num_heads, num_kv_heads, head_dim, q_norm_weight
 
 
 def paged_attention(q, kv_cache, *, positions, token_seq, block_table, scale, window=None, step=None,
-                    status=None):
+                    status=None, sink=None, out_scale=1.0):
+    """``sink``: a logit that joins the softmax (one more column) without a value; ``out_scale``: a factor."""
     t, hq, d = q.shape
     _, _, hkv, page_size, _ = kv_cache.shape
     group = hq // hkv
@@ -117,8 +118,10 @@ def paged_attention(q, kv_cache, *, positions, token_seq, block_table, scale, wi
         v = _acc(kv_cache[1, pages, :, js % page_size, :])
         qi = _acc(q[i]).view(hkv, group, d)
         s = torch.einsum("hgd,nhd->hgn", qi, k) * scale
-        p = torch.softmax(s, dim=-1)
-        out[i] = torch.einsum("hgn,nhd->hgd", p, v).reshape(hq, d).to(q.dtype)
+        if sink is not None:
+            s = torch.cat([s, torch.full_like(s[..., :1], float(sink))], dim=-1)
+        p = torch.softmax(s, dim=-1)[..., :js.shape[0]]
+        out[i] = (out_scale * torch.einsum("hgn,nhd->hgd", p, v)).reshape(hq, d).to(q.dtype)
     return out.view(t, hq * d)
 
 

@@ -59,6 +59,8 @@ struct PairParams {
     const int* block_table;
     int max_blocks, hq, hkv, page_size, num_pages, window;
     float scale_log2;
+    int has_sink;                    // the softmax denominator holds one more term 2^sink_log2 that has no value
+    float sink_log2, out_scale;      // out_scale multiplies the output before its rounding
     int* status;
 };
 
@@ -396,7 +398,8 @@ prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap q_map, const _
         if (ok && num_x > 0) {
             if (mbar_wait(o_full(x), (num_x - 1) & 1u, abort_flag, p.status, 47)) {
                 tmem_fence_after();
-                const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+                const float l_all = p.has_sink ? l_run + ex2(p.sink_log2 - m_ref) : l_run;      // every score far below the sink: inf, 0
+                const float inv = l_all > 0.f ? p.out_scale / l_all : 0.f;
                 const int rows_x = min(QM, nrows - x * QM);
                 __nv_bfloat16* dst = p.out + ((size_t)(row0 + x * QM + r) * p.hq + head) * D;
                 uint32_t orow[32];
@@ -436,10 +439,11 @@ TI_API int ti_attention_prefill_pair_rows() { return 2 * QM; }
 // Prefill attention on tcgen05, two query tiles a CTA. `tiles`: num_tiles int4 {request index in the step,
 // first flat row, rows (<= 256), position of the first row}, every tile inside one request's portion.
 // q [T, Hq, D], out [T, Hq * D], kv_cache [2, num_pages, Hkv, page_size, D]; page_size 16, 32 or a multiple of 64.
-TI_API int ti_attention_prefill_pair_bf16(void* out, const void* q, const void* kv_cache, const int* tiles, int num_tiles,
-                                          int num_tokens, const int* block_table, int max_blocks, int hq, int hkv, int d,
-                                          int page_size, int num_pages, float scale, int window, int* status,
-                                          cudaStream_t stream) {
+// has_sink: exp(sink) joins every softmax denominator without a value; out_scale: a factor on the output.
+TI_API int ti_attention_prefill_pair_sink_bf16(void* out, const void* q, const void* kv_cache, const int* tiles, int num_tiles,
+                                               int num_tokens, const int* block_table, int max_blocks, int hq, int hkv, int d,
+                                               int page_size, int num_pages, float scale, int window, int has_sink,
+                                               float sink, float out_scale, int* status, cudaStream_t stream) {
     TI_REQUIRE(d == 64 || d == 128, "attention_prefill_pair: head_dim %d is not 64 or 128", d);
     TI_REQUIRE(hq > 0 && hkv > 0 && hq % hkv == 0, "attention_prefill_pair: bad head counts");
     TI_REQUIRE(num_tiles <= 65535, "attention_prefill_pair: more than 65535 tiles in one step");
@@ -453,6 +457,7 @@ TI_API int ti_attention_prefill_pair_bf16(void* out, const void* q, const void* 
     p.out = (__nv_bfloat16*)out; p.tiles = tiles; p.block_table = block_table; p.max_blocks = max_blocks;
     p.hq = hq; p.hkv = hkv; p.page_size = page_size; p.num_pages = num_pages; p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+    p.has_sink = has_sink ? 1 : 0; p.sink_log2 = sink * 1.4426950408889634f; p.out_scale = out_scale;
     dim3 grid(hq, num_tiles);
     if (d == 128) {
         static bool once = false;
@@ -473,4 +478,12 @@ TI_API int ti_attention_prefill_pair_bf16(void* out, const void* q, const void* 
     }
     TI_CHECK_LAUNCH("attention_prefill_pair");
     return 0;
+}
+
+TI_API int ti_attention_prefill_pair_bf16(void* out, const void* q, const void* kv_cache, const int* tiles, int num_tiles,
+                                          int num_tokens, const int* block_table, int max_blocks, int hq, int hkv, int d,
+                                          int page_size, int num_pages, float scale, int window, int* status,
+                                          cudaStream_t stream) {
+    return ti_attention_prefill_pair_sink_bf16(out, q, kv_cache, tiles, num_tiles, num_tokens, block_table, max_blocks, hq, hkv,
+                                               d, page_size, num_pages, scale, window, 0, 0.f, 1.f, status, stream);
 }

@@ -8,7 +8,8 @@
 //   short_conv        : out[t][c] = act(bias[c] + sum_j w[c][j] * in[t - (taps - 1 - j)][c]),  act: none or silu
 //   conv_qkv_append   : the same on the packed rows [q | k | v] of an attention layer, without bias or activation;
 //                       q is multiplied by its position's temperature 1 + coef * ln(floor((p + 1) / every) + 1)
-//                       and stored as [T][Hq][d]; k and v go to the token's row of its page: [k (d) | v (dv)]
+//                       and stored as [T][Hq][d]; k and v go to the token's row of its page: [k (d) | v (dv)], or,
+//                       where keys and values have the same size, to the two planes [keys][values] of the cache
 //   conv_state_update : the step's last taps - 1 inputs of every request become its history
 //   attention_rows    : causal attention of q over such pages, float32 arithmetic, any sizes; optionally the
 //                       softmax denominator holds one more term exp(sink) that has no value ("sink")
@@ -31,12 +32,21 @@ __device__ __forceinline__ float conv_at(const T* __restrict__ in, int ld_in, in
     return acc;
 }
 
+// A step in which every request brings ONE token: the thread that made the token's output is the only one that
+// read this channel's history, so it may also move the history on by one (oldest out, the token's input in).
+__device__ __forceinline__ void conv_shift_history(float* __restrict__ hist, int width, int c, int taps, float newest) {
+    float kept[SC_MAX_TAPS];
+    for (int j = 1; j < taps - 1; ++j) kept[j] = hist[(size_t)j * width + c];
+    for (int j = 1; j < taps - 1; ++j) hist[(size_t)(j - 1) * width + c] = kept[j];
+    hist[(size_t)(taps - 2) * width + c] = newest;
+}
+
 template <typename T>
 __global__ void short_conv_kernel(T* __restrict__ out, const T* __restrict__ in, int ld_in, int in_off,
                                   const float* __restrict__ state, long long slot_stride, const float* __restrict__ w,
                                   const float* __restrict__ bias, const int* __restrict__ token_seq,
                                   const int* __restrict__ cu_seqlens, const int* __restrict__ state_slots, int width,
-                                  int taps, int act) {
+                                  int taps, int act, int shift_history) {
     ti_grid_launch_dependents();
     ti_grid_wait();
     const int t = blockIdx.y;
@@ -46,25 +56,30 @@ __global__ void short_conv_kernel(T* __restrict__ out, const T* __restrict__ in,
     const int local = t - cu_seqlens[seq];
     const float* hist = state + (size_t)state_slots[seq] * slot_stride;
     float v = conv_at(in, ld_in, in_off + c, t, local, hist, width, c, w, taps);
+    if (shift_history && taps > 1)
+        conv_shift_history(const_cast<float*>(hist), width, c, taps, to_f32(in[(size_t)t * ld_in + in_off + c]));
     if (bias) v += bias[c];
     if (act == 1) v = v / (1.f + expf(-v));
     out[(size_t)t * width + c] = from_f32<T>(v);
 }
 
-TI_API int ti_short_conv(void* out, const void* in, int ld_in, int in_off, const float* state, long long slot_stride,
+// shift_history: every request of the step brings one token, and the kernel also moves the histories on (otherwise
+// conv_state_update does, afterwards).
+TI_API int ti_short_conv(void* out, const void* in, int ld_in, int in_off, float* state, long long slot_stride,
                          const float* w, const float* bias, const int* token_seq, const int* cu_seqlens,
-                         const int* state_slots, int num_tokens, int width, int taps, int act, int dtype, cudaStream_t stream) {
+                         const int* state_slots, int num_tokens, int width, int taps, int act, int shift_history, int dtype,
+                         cudaStream_t stream) {
     TI_REQUIRE(num_tokens >= 0 && width > 0 && taps >= 1 && taps <= SC_MAX_TAPS, "short_conv: bad sizes (taps 1..%d)", SC_MAX_TAPS);
     TI_REQUIRE(num_tokens <= 65535, "short_conv: more than 65535 tokens in one step");
     TI_REQUIRE(act == 0 || act == 1, "short_conv: unknown activation %d", act);
     if (num_tokens == 0) return 0;
     dim3 grid((width + 127) / 128, num_tokens);
     if (dtype == TI_F32)
-        ti_launch(short_conv_kernel<float>, grid, 128, 0, stream, (float*)out, (const float*)in, ld_in, in_off, state, slot_stride,
-                  w, bias, token_seq, cu_seqlens, state_slots, width, taps, act);
+        ti_launch(short_conv_kernel<float>, grid, 128, 0, stream, (float*)out, (const float*)in, ld_in, in_off, (const float*)state, slot_stride,
+                  w, bias, token_seq, cu_seqlens, state_slots, width, taps, act, shift_history);
     else if (dtype == TI_BF16)
         ti_launch(short_conv_kernel<__nv_bfloat16>, grid, 128, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)in, ld_in,
-                  in_off, state, slot_stride, w, bias, token_seq, cu_seqlens, state_slots, width, taps, act);
+                  in_off, (const float*)state, slot_stride, w, bias, token_seq, cu_seqlens, state_slots, width, taps, act, shift_history);
     else TI_REQUIRE(false, "short_conv: unknown dtype %d", dtype);
     TI_CHECK_LAUNCH("short_conv");
     return 0;
@@ -117,7 +132,7 @@ __global__ void conv_qkv_append_kernel(T* __restrict__ q_out, T* __restrict__ ca
                                        const int* __restrict__ token_seq, const int* __restrict__ cu_seqlens,
                                        const int* __restrict__ state_slots, const int* __restrict__ block_table,
                                        int max_blocks, int hq, int hkv, int d, int dv, int page_size, int num_pages,
-                                       int* __restrict__ status) {
+                                       int row_stride, long long v_off, int shift_history, int* __restrict__ status) {
     ti_grid_launch_dependents();
     ti_grid_wait();
     const int t = blockIdx.y;
@@ -129,6 +144,7 @@ __global__ void conv_qkv_append_kernel(T* __restrict__ q_out, T* __restrict__ ca
     const float* hist = taps > 1 ? state + (size_t)state_slots[seq] * slot_stride : nullptr;
     float v = taps > 1 ? conv_at(qkv, width, c, t, local, hist, width, c, w, taps)
                        : (w ? w[c] : 1.f) * to_f32(qkv[(size_t)t * width + c]);
+    if (shift_history && taps > 1) conv_shift_history(const_cast<float*>(hist), width, c, taps, to_f32(qkv[(size_t)t * width + c]));
     const int pos = positions[t];
     if (c < cq) {
         if (temp_every > 0) v *= 1.f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.f);
@@ -142,18 +158,24 @@ __global__ void conv_qkv_append_kernel(T* __restrict__ q_out, T* __restrict__ ca
         if (status) atomicExch(status, 1);                 // a token without a page
         return;
     }
-    int head, i, off;
-    if (c < cq + ck) { head = (c - cq) / d; i = (c - cq) % d; off = i; }
-    else { head = (c - cq - ck) / dv; i = (c - cq - ck) % dv; off = d + i; }
-    cache[(((size_t)page * hkv + head) * page_size + pos % page_size) * (d + dv) + off] = from_f32<T>(v);
+    int head;
+    long long off;
+    if (c < cq + ck) { head = (c - cq) / d; off = (c - cq) % d; }
+    else { head = (c - cq - ck) / dv; off = v_off + (c - cq - ck) % dv; }
+    cache[(((size_t)page * hkv + head) * page_size + pos % page_size) * row_stride + off] = from_f32<T>(v);
 }
 
 // w: float32 [width][taps] over the packed channels (may be null with taps == 1: no convolution at all).
-TI_API int ti_conv_qkv_append(void* q_out, void* cache, const void* qkv, const float* state, long long slot_stride,
+// planes 1: cache [pages][hkv][page_size][d + dv]; planes 2 (d == dv): [2][pages][hkv][page_size][d].
+// shift_history: as in ti_short_conv.
+TI_API int ti_conv_qkv_append(void* q_out, void* cache, const void* qkv, float* state, long long slot_stride,
                               const float* w, int taps, float temp_coef, int temp_every, const int* positions,
                               const int* token_seq, const int* cu_seqlens, const int* state_slots, const int* block_table,
                               int max_blocks, int num_tokens, int hq, int hkv, int d, int dv, int page_size, int num_pages,
-                              int* status, int dtype, cudaStream_t stream) {
+                              int planes, int shift_history, int* status, int dtype, cudaStream_t stream) {
+    TI_REQUIRE(planes == 1 || (planes == 2 && d == dv), "conv_qkv_append: two planes need keys and values of one size");
+    const int row_stride = planes == 2 ? d : d + dv;
+    const long long v_off = planes == 2 ? (long long)num_pages * hkv * page_size * d : d;
     TI_REQUIRE(num_tokens >= 0 && hq > 0 && hkv > 0 && d > 0 && dv > 0 && taps >= 1 && taps <= SC_MAX_TAPS,
                "conv_qkv_append: bad sizes (taps 1..%d)", SC_MAX_TAPS);
     TI_REQUIRE(taps == 1 || (w && state), "conv_qkv_append: a convolution needs its weights and the history");
@@ -163,13 +185,14 @@ TI_API int ti_conv_qkv_append(void* q_out, void* cache, const void* qkv, const f
     const int width = hq * d + hkv * (d + dv);
     dim3 grid((width + 127) / 128, num_tokens);
     if (dtype == TI_F32)
-        ti_launch(conv_qkv_append_kernel<float>, grid, 128, 0, stream, (float*)q_out, (float*)cache, (const float*)qkv, state,
+        ti_launch(conv_qkv_append_kernel<float>, grid, 128, 0, stream, (float*)q_out, (float*)cache, (const float*)qkv, (const float*)state,
                   slot_stride, w, taps, temp_coef, temp_every, positions, token_seq, cu_seqlens, state_slots, block_table,
-                  max_blocks, hq, hkv, d, dv, page_size, num_pages, status);
+                  max_blocks, hq, hkv, d, dv, page_size, num_pages, row_stride, v_off, shift_history, status);
     else if (dtype == TI_BF16)
         ti_launch(conv_qkv_append_kernel<__nv_bfloat16>, grid, 128, 0, stream, (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache,
-                  (const __nv_bfloat16*)qkv, state, slot_stride, w, taps, temp_coef, temp_every, positions, token_seq,
-                  cu_seqlens, state_slots, block_table, max_blocks, hq, hkv, d, dv, page_size, num_pages, status);
+                  (const __nv_bfloat16*)qkv, (const float*)state, slot_stride, w, taps, temp_coef, temp_every, positions, token_seq,
+                  cu_seqlens, state_slots, block_table, max_blocks, hq, hkv, d, dv, page_size, num_pages, row_stride, v_off,
+                  shift_history, status);
     else TI_REQUIRE(false, "conv_qkv_append: unknown dtype %d", dtype);
     TI_CHECK_LAUNCH("conv_qkv_append");
     return 0;
@@ -185,8 +208,8 @@ template <typename T>
 __global__ void __launch_bounds__(AR_THREADS) attention_rows_kernel(
     T* __restrict__ out, const T* __restrict__ q, const T* __restrict__ cache, const int* __restrict__ positions,
     const int* __restrict__ token_seq, const int* __restrict__ block_table, int max_blocks, int hq, int hkv, int d, int dv,
-    int page_size, int num_pages, float scale, int window, int has_sink, float sink, float out_scale,
-    int* __restrict__ status) {
+    int page_size, int num_pages, int row, long long v_off, float scale, int window, int has_sink, float sink,
+    float out_scale, int* __restrict__ status) {
     __shared__ float qs[AR_MAX_D];
     __shared__ float p[AR_THREADS];
     __shared__ long long row_off[AR_THREADS];
@@ -198,7 +221,6 @@ __global__ void __launch_bounds__(AR_THREADS) attention_rows_kernel(
     const int pos = positions[t];
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int kvh = h / (hq / hkv);
-    const int row = d + dv;
     const int* table = block_table + (size_t)token_seq[t] * max_blocks;
     const T* qrow = q + ((size_t)t * hq + h) * d;
     for (int i = tid; i < d; i += AR_THREADS) qs[i] = to_f32(qrow[i]);
@@ -240,8 +262,8 @@ __global__ void __launch_bounds__(AR_THREADS) attention_rows_kernel(
                 const long long o = row_off[jj];
                 if (o < 0) continue;
                 const float pv = p[jj];
-                acc0 = fmaf(pv, to_f32(cache[o + d + tid]), acc0);
-                if (tid + AR_THREADS < dv) acc1 = fmaf(pv, to_f32(cache[o + d + tid + AR_THREADS]), acc1);
+                acc0 = fmaf(pv, to_f32(cache[o + v_off + tid]), acc0);
+                if (tid + AR_THREADS < dv) acc1 = fmaf(pv, to_f32(cache[o + v_off + tid + AR_THREADS]), acc1);
             }
         }
         __syncthreads();
@@ -252,11 +274,15 @@ __global__ void __launch_bounds__(AR_THREADS) attention_rows_kernel(
     if (tid + AR_THREADS < dv) orow[tid + AR_THREADS] = from_f32<T>(acc1 * inv);
 }
 
-// cache: [pages][hkv][page_size][d + dv]; out: [T][hq * dv], multiplied by out_scale before its one rounding.
+// planes 1: cache [pages][hkv][page_size][d + dv]; planes 2 (d == dv): [2][pages][hkv][page_size][d].
+// out: [T][hq * dv], multiplied by out_scale before its one rounding.
 TI_API int ti_attention_rows(void* out, const void* q, const void* cache, const int* positions, const int* token_seq,
                              const int* block_table, int max_blocks, int num_tokens, int hq, int hkv, int d, int dv,
-                             int page_size, int num_pages, float scale, int window, int has_sink, float sink,
+                             int page_size, int num_pages, int planes, float scale, int window, int has_sink, float sink,
                              float out_scale, int* status, int dtype, cudaStream_t stream) {
+    TI_REQUIRE(planes == 1 || (planes == 2 && d == dv), "attention_rows: two planes need keys and values of one size");
+    const int row = planes == 2 ? d : d + dv;
+    const long long v_off = planes == 2 ? (long long)num_pages * hkv * page_size * d : d;
     TI_REQUIRE(d > 0 && d <= AR_MAX_D && dv > 0 && dv <= AR_MAX_D, "attention_rows: head sizes %d / %d not in 1..%d", d, dv, AR_MAX_D);
     TI_REQUIRE(hq > 0 && hkv > 0 && hq % hkv == 0, "attention_rows: %d query heads do not group over %d kv heads", hq, hkv);
     TI_REQUIRE(page_size > 0 && num_tokens >= 0 && window >= 0, "attention_rows: bad sizes");
@@ -265,12 +291,12 @@ TI_API int ti_attention_rows(void* out, const void* q, const void* cache, const 
     dim3 grid(hq, num_tokens);
     if (dtype == TI_F32)
         ti_launch(attention_rows_kernel<float>, grid, AR_THREADS, 0, stream, (float*)out, (const float*)q, (const float*)cache,
-                  positions, token_seq, block_table, max_blocks, hq, hkv, d, dv, page_size, num_pages, scale, window, has_sink,
-                  sink, out_scale, status);
+                  positions, token_seq, block_table, max_blocks, hq, hkv, d, dv, page_size, num_pages, row, v_off, scale, window,
+                  has_sink, sink, out_scale, status);
     else if (dtype == TI_BF16)
         ti_launch(attention_rows_kernel<__nv_bfloat16>, grid, AR_THREADS, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)q,
                   (const __nv_bfloat16*)cache, positions, token_seq, block_table, max_blocks, hq, hkv, d, dv, page_size,
-                  num_pages, scale, window, has_sink, sink, out_scale, status);
+                  num_pages, row, v_off, scale, window, has_sink, sink, out_scale, status);
     else TI_REQUIRE(false, "attention_rows: unknown dtype %d", dtype);
     TI_CHECK_LAUNCH("attention_rows");
     return 0;

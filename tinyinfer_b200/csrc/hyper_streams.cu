@@ -44,9 +44,40 @@ TI_API int ti_streams_embed(float* X, const void* table, const int* ids, int num
     return 0;
 }
 
+// VEC neighbouring features at a time: 16-byte loads and stores of the float32 streams where rows allow it.
+template <int VEC> struct HsVec;
+template <> struct HsVec<1> {
+    static __device__ __forceinline__ void load(const float* p, float* v) { v[0] = *p; }
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* v) { v[0] = __bfloat162float(*p); }
+    static __device__ __forceinline__ void store(float* p, const float* v) { *p = v[0]; }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* v) { *p = __float2bfloat16_rn(v[0]); }
+};
+template <> struct HsVec<4> {
+    static __device__ __forceinline__ void load(const float* p, float* v) {
+        const float4 f = *reinterpret_cast<const float4*>(p);
+        v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+    }
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* v) {
+        const uint2 u = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+        v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+    }
+    static __device__ __forceinline__ void store(float* p, const float* v) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* v) {
+        uint2 u;
+        *reinterpret_cast<__nv_bfloat162*>(&u.x) = __floats2bfloat162_rn(v[0], v[1]);
+        *reinterpret_cast<__nv_bfloat162*>(&u.y) = __floats2bfloat162_rn(v[2], v[3]);
+        *reinterpret_cast<uint2*>(p) = u;
+    }
+};
+
 // TY: what the pending sublayer output y is stored in; TH: what h is stored in.
-template <typename TY, typename TH>
-__global__ void streams_step_kernel(float* __restrict__ X, const TY* __restrict__ y, const float* __restrict__ c_mix,
+// NS: the most streams this instance is unrolled for (the arrays below live in registers).
+template <typename TY, typename TH, int VEC, int NS>
+__global__ void __launch_bounds__(VEC == 4 ? 256 : 512) streams_step_kernel(float* __restrict__ X, const TY* __restrict__ y, const float* __restrict__ c_mix,
                                     const float* __restrict__ c_out, const float* __restrict__ c_in,
                                     const float* __restrict__ norm_w, float eps, TH* __restrict__ h,
                                     const int* __restrict__ rows, int num_tokens, int width, int streams) {
@@ -64,45 +95,57 @@ __global__ void streams_step_kernel(float* __restrict__ X, const TY* __restrict_
     const int r = blockIdx.x;
     const int t = rows ? rows[r] : r;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        float x[HS_MAX_STREAMS];
+    for (int i = threadIdx.x * VEC; i < width; i += blockDim.x * VEC) {
+        float x[NS][VEC];
 #pragma unroll
-        for (int s = 0; s < HS_MAX_STREAMS; ++s)
-            if (s < streams) x[s] = X[((size_t)s * num_tokens + t) * width + i];
+        for (int s = 0; s < NS; ++s)
+            if (s < streams) HsVec<VEC>::load(X + ((size_t)s * num_tokens + t) * width + i, x[s]);
         if (y) {
-            const float yv = to_f32(y[(size_t)t * width + i]);
-            float fresh[HS_MAX_STREAMS];
+            float yv[VEC], fresh[NS][VEC];
+            HsVec<VEC>::load(y + (size_t)t * width + i, yv);
 #pragma unroll
-            for (int to = 0; to < HS_MAX_STREAMS; ++to) {
+            for (int to = 0; to < NS; ++to) {
                 if (to < streams) {
-                    float acc = 0.f;
 #pragma unroll
-                    for (int s = 0; s < HS_MAX_STREAMS; ++s)
-                        if (s < streams) acc = fmaf(mix[s * streams + to], x[s], acc);
-                    fresh[to] = fmaf(cout_s[to], yv, acc);
+                    for (int e = 0; e < VEC; ++e) {
+                        float acc = 0.f;
+#pragma unroll
+                        for (int s = 0; s < NS; ++s)
+                            if (s < streams) acc = fmaf(mix[s * streams + to], x[s][e], acc);
+                        fresh[to][e] = fmaf(cout_s[to], yv[e], acc);
+                    }
                 }
             }
 #pragma unroll
-            for (int s = 0; s < HS_MAX_STREAMS; ++s)
+            for (int s = 0; s < NS; ++s)
                 if (s < streams) {
-                    x[s] = fresh[s];
-                    X[((size_t)s * num_tokens + t) * width + i] = fresh[s];
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) x[s][e] = fresh[s][e];
+                    HsVec<VEC>::store(X + ((size_t)s * num_tokens + t) * width + i, fresh[s]);
                 }
         }
         if (h) {
-            float u = 0.f;
 #pragma unroll
-            for (int s = 0; s < HS_MAX_STREAMS; ++s)
-                if (s < streams) u = fmaf(cin_s[s], x[s], u);
-            urow[i] = u;
-            ss += u * u;
+            for (int e = 0; e < VEC; ++e) {
+                float u = 0.f;
+#pragma unroll
+                for (int s = 0; s < NS; ++s)
+                    if (s < streams) u = fmaf(cin_s[s], x[s][e], u);
+                urow[i + e] = u;
+                ss += u * u;
+            }
         }
     }
     if (!h) return;
     ss = block_sum(ss, red);
     const float inv = rsqrtf(ss / (float)width + eps);
-    for (int i = threadIdx.x; i < width; i += blockDim.x)
-        h[(size_t)r * width + i] = from_f32<TH>(norm_w[i] * urow[i] * inv);
+    for (int i = threadIdx.x * VEC; i < width; i += blockDim.x * VEC) {
+        float w[VEC], o[VEC];
+        HsVec<VEC>::load(norm_w + i, w);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) o[e] = w[e] * urow[i + e] * inv;
+        HsVec<VEC>::store(h + (size_t)r * width + i, o);
+    }
 }
 
 // y (may be null: nothing pending) with c_mix [S][S] (indexed [from][to]) and c_out [S]; h (may be null: only the
@@ -116,48 +159,76 @@ TI_API int ti_streams_step(float* X, const void* y, const float* c_mix, const fl
     TI_REQUIRE(!y || (c_mix && c_out), "streams_step: an update needs its coefficients");
     TI_REQUIRE(!h || (c_in && norm_w), "streams_step: a read needs its coefficients and the norm's weight");
     if (num_rows == 0 || (!y && !h)) return 0;
+    const bool wide = width % 4 == 0 && ((uintptr_t)X | (uintptr_t)y | (uintptr_t)h | (uintptr_t)norm_w) % 16 == 0 &&
+                      ((size_t)num_tokens * width) % 4 == 0;
     int threads = 64;
-    while (threads < 512 && threads * 4 < width) threads <<= 1;
+    while (threads < (wide ? 256 : 512) && threads * 4 < width) threads <<= 1;
     const size_t smem = h ? (size_t)width * sizeof(float) : 0;
     typedef __nv_bfloat16 B;
-#define TI_STEP(TY, TH)                                                                                              \
-    ti_launch(streams_step_kernel<TY, TH>, num_rows, threads, smem, stream, X, (const TY*)y, c_mix, c_out, c_in, norm_w, \
-              eps, (TH*)h, rows, num_tokens, width, streams)
+#define TI_STEP_N(TY, TH, VEC, NS)                                                                                        \
+    ti_launch(streams_step_kernel<TY, TH, VEC, NS>, num_rows, threads, smem, stream, X, (const TY*)y, c_mix, c_out, c_in, \
+              norm_w, eps, (TH*)h, rows, num_tokens, width, streams)
+#define TI_STEP_V(TY, TH, VEC)                             \
+    do {                                                   \
+        if (streams == 1) TI_STEP_N(TY, TH, VEC, 1);       \
+        else if (streams == 2) TI_STEP_N(TY, TH, VEC, 2);  \
+        else if (streams <= 4) TI_STEP_N(TY, TH, VEC, 4);  \
+        else TI_STEP_N(TY, TH, VEC, HS_MAX_STREAMS);       \
+    } while (0)
+#define TI_STEP(TY, TH)                    \
+    do {                                   \
+        if (wide) TI_STEP_V(TY, TH, 4);    \
+        else TI_STEP_V(TY, TH, 1);         \
+    } while (0)
     if (y_dtype == TI_F32 && h_dtype == TI_F32) TI_STEP(float, float);
     else if (y_dtype == TI_F32 && h_dtype == TI_BF16) TI_STEP(float, B);
     else if (y_dtype == TI_BF16 && h_dtype == TI_BF16) TI_STEP(B, B);
     else if (y_dtype == TI_BF16 && h_dtype == TI_F32) TI_STEP(B, float);
     else TI_REQUIRE(false, "streams_step: unknown dtypes %d, %d", y_dtype, h_dtype);
 #undef TI_STEP
+#undef TI_STEP_V
+#undef TI_STEP_N
     TI_CHECK_LAUNCH("streams_step");
     return 0;
 }
 
 // ------------------------------------------------------------------ activation and scaling
 // kind 0: the exact gelu 0.5 z (1 + erf(z / sqrt 2)); 1: its tanh form. In place or not; float32 arithmetic.
+__device__ __forceinline__ float gelu_of(float z, int kind) {
+    return kind == 0 ? 0.5f * z * (1.f + erff(z * 0.70710678118654752f))
+                     : 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// 16 bytes a thread a trip where the tensors start on 16-byte boundaries; what is left at the end one by one.
 template <typename T>
-__global__ void gelu_kernel(T* __restrict__ out, const T* __restrict__ x, size_t n, int kind) {
+__global__ void gelu_kernel(T* __restrict__ out, const T* __restrict__ x, size_t n, int kind, int wide) {
     ti_grid_launch_dependents();
     ti_grid_wait();
+    constexpr int VEC = 16 / sizeof(T);
     const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-        const float z = to_f32(x[i]);
-        const float v = kind == 0 ? 0.5f * z * (1.f + erff(z * 0.70710678118654752f))
-                                  : 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
-        out[i] = from_f32<T>(v);
+    const size_t first = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t groups = wide ? n / VEC : 0;
+    for (size_t gi = first; gi < groups; gi += stride) {
+        uint4 raw = reinterpret_cast<const uint4*>(x)[gi];
+        T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) e[j] = from_f32<T>(gelu_of(to_f32(e[j]), kind));
+        reinterpret_cast<uint4*>(out)[gi] = raw;
     }
+    for (size_t i = groups * VEC + first; i < n; i += stride) out[i] = from_f32<T>(gelu_of(to_f32(x[i]), kind));
 }
 
 TI_API int ti_gelu(void* out, const void* x, long long n, int kind, int dtype, cudaStream_t stream) {
     TI_REQUIRE(n >= 0 && (kind == 0 || kind == 1), "gelu: bad arguments");
     if (n == 0) return 0;
     const int threads = 256;
-    const long long want = (n + threads - 1) / threads;
+    const int wide = ((uintptr_t)out | (uintptr_t)x) % 16 == 0;
+    const long long want = (n / (dtype == TI_F32 ? 4 : 8) + threads - 1) / threads + 1;
     const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
     if (dtype == TI_F32)
-        ti_launch(gelu_kernel<float>, blocks, threads, 0, stream, (float*)out, (const float*)x, (size_t)n, kind);
+        ti_launch(gelu_kernel<float>, blocks, threads, 0, stream, (float*)out, (const float*)x, (size_t)n, kind, wide);
     else if (dtype == TI_BF16)
-        ti_launch(gelu_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)x, (size_t)n, kind);
+        ti_launch(gelu_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)x, (size_t)n, kind, wide);
     else TI_REQUIRE(false, "gelu: unknown dtype %d", dtype);
     TI_CHECK_LAUNCH("gelu");
     return 0;

@@ -16,6 +16,12 @@
 // tokens of the request are walked in order; q, k and the decays of a few tokens at a time are staged in shared
 // memory by the whole block.
 //
+// Long portions are cut into stretches that run side by side (grid z), since the recurrence composes: a stretch is
+// (A, B) = (the product of its decays, its own scan from a zero state). Pass 1 scans every stretch from zero and
+// leaves (A, B); a fold walks a request's stretches in order, S <- A S + B, leaves each stretch's true starting state
+// where its B was and the request's new state in its slot; pass 2 scans every stretch again from its true start and
+// writes the outputs. Twice the arithmetic, as many times the blocks as there are stretches.
+//
 //   gated_group_norm : out = scale * w * n(y) * silu(gate)  or  scale * w * n(y * silu(gate)),  n: every group of
 //                      `group` features divided by its root mean square (float32), one rounding
 #include "common.cuh"
@@ -39,9 +45,13 @@ struct LinearScanArgs {
     float q_scale;
     const int *cu_seqlens, *state_slots;
     int heads, groups, dk, dv, kp, chunk;
+    int stretches;            // > 1: grid z is the stretch; part_b [request][stretch][H][dv][dk], part_a [request][stretch][H][dk]
+    float *part_b, *part_a;
 };
 
-template <typename T, int KPT>
+// MODE 0: from the slot's state to the slot's state, with outputs; 1: a stretch from zero, leaves (A, B), no outputs;
+// 2: a stretch from the start the fold left, with outputs.
+template <typename T, int KPT, int MODE>
 __global__ void __launch_bounds__(LS_WARPS * 32) linear_scan_kernel(LinearScanArgs a) {
     extern __shared__ float smem[];
     ti_grid_launch_dependents();
@@ -56,7 +66,13 @@ __global__ void __launch_bounds__(LS_WARPS * 32) linear_scan_kernel(LinearScanAr
     const int col = cb * cols_per_block + warp * cols_per_warp + lane / KP;
     const bool col_ok = col < a.dv;
     const int g = h / (a.heads / a.groups);
-    const int row0 = a.cu_seqlens[seq], row1 = a.cu_seqlens[seq + 1];
+    int row0 = a.cu_seqlens[seq], row1 = a.cu_seqlens[seq + 1];
+    if (MODE != 0) {                                     // this block's stretch of the request's tokens
+        const int n = row1 - row0, len = (n + a.stretches - 1) / a.stretches;
+        const int first = row0 + min(n, (int)blockIdx.z * len);
+        row1 = row0 + min(n, ((int)blockIdx.z + 1) * len);
+        row0 = first;
+    }
     float* sq = smem;                                    // [chunk][dkp]
     float* sk = sq + (size_t)a.chunk * dkp;
     float* sa = sk + (size_t)a.chunk * dkp;
@@ -65,12 +81,15 @@ __global__ void __launch_bounds__(LS_WARPS * 32) linear_scan_kernel(LinearScanAr
     const T* k = (const T*)a.k;
     const T* v = (const T*)a.v;
 
-    float* srow = a.state + (size_t)a.state_slots[seq] * a.slot_stride + ((size_t)h * a.dv + (col_ok ? col : 0)) * a.dk;
-    float S[KPT];
+    const size_t in_head = ((size_t)h * a.dv + (col_ok ? col : 0)) * a.dk;
+    float* srow = MODE == 0 ? a.state + (size_t)a.state_slots[seq] * a.slot_stride + in_head
+                            : a.part_b + ((size_t)seq * a.stretches + blockIdx.z) * a.heads * a.dv * a.dk + in_head;
+    float S[KPT], A[MODE == 1 ? KPT : 1];
 #pragma unroll
     for (int r = 0; r < KPT; ++r) {
         const int idx = r * KP + kpart;
-        S[r] = (col_ok && idx < a.dk) ? srow[idx] : 0.f;
+        S[r] = (MODE != 1 && col_ok && idx < a.dk) ? srow[idx] : 0.f;
+        if (MODE == 1) A[r] = 1.f;
     }
     const float skip = a.skip ? a.skip[h] : 0.f;
     float rate = 0.f, bias = 0.f;
@@ -116,12 +135,16 @@ __global__ void __launch_bounds__(LS_WARPS * 32) linear_scan_kernel(LinearScanAr
 #pragma unroll
             for (int r = 0; r < KPT; ++r) {
                 S[r] = fmaf(pa[r * KP], S[r], pk[r * KP] * vv);
-                o = fmaf(S[r], pq[r * KP], o);
+                if (MODE == 1) A[r] *= pa[r * KP];
+                else o = fmaf(S[r], pq[r * KP], o);
             }
-            for (int off = 1; off < KP; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
-            if (kpart == 0 && col_ok) a.y[(size_t)(t0 + tt) * a.heads * a.dv + h * a.dv + col] = fmaf(skip, vv, o);
+            if (MODE != 1) {
+                for (int off = 1; off < KP; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+                if (kpart == 0 && col_ok) a.y[(size_t)(t0 + tt) * a.heads * a.dv + h * a.dv + col] = fmaf(skip, vv, o);
+            }
         }
     }
+    if (MODE == 2) return;
     if (col_ok) {
 #pragma unroll
         for (int r = 0; r < KPT; ++r) {
@@ -129,20 +152,59 @@ __global__ void __launch_bounds__(LS_WARPS * 32) linear_scan_kernel(LinearScanAr
             if (idx < a.dk) srow[idx] = S[r];
         }
     }
+    if (MODE == 1 && cb == 0 && warp == 0 && lane < KP) {           // the stretch's product of decays, once a head
+        float* arow = a.part_a + (((size_t)seq * a.stretches + blockIdx.z) * a.heads + h) * a.dk;
+#pragma unroll
+        for (int r = 0; r < KPT; ++r) {
+            const int idx = r * KP + kpart;
+            if (idx < a.dk) arow[idx] = A[r];
+        }
+    }
+}
+
+// A request's stretches in order: S <- A S + B. Each stretch's B becomes the state it starts from; the slot gets
+// the state after the last. One thread per element of a request's states.
+__global__ void linear_scan_fold_kernel(float* __restrict__ state, long long slot_stride, float* __restrict__ part_b,
+                                        const float* __restrict__ part_a, const int* __restrict__ state_slots,
+                                        int stretches, int heads, int dk, int dv) {
+    ti_grid_launch_dependents();
+    ti_grid_wait();
+    const int per = heads * dv * dk;
+    const int e = blockIdx.x * blockDim.x + threadIdx.x, seq = blockIdx.y;
+    if (e >= per) return;
+    const int idx = e % dk, h = e / (dv * dk);
+    float* slot = state + (size_t)state_slots[seq] * slot_stride;
+    float S = slot[e];
+    for (int k = 0; k < stretches; ++k) {
+        const size_t part = (size_t)seq * stretches + k;
+        const float b = part_b[part * per + e];
+        const float a = part_a[(part * heads + h) * dk + idx];
+        part_b[part * per + e] = S;
+        S = fmaf(a, S, b);
+    }
+    slot[e] = S;
+}
+
+TI_API long long ti_linear_scan_scratch_floats(int num_seqs, int heads, int dk, int dv, int stretches) {
+    return stretches > 1 ? (long long)num_seqs * stretches * heads * dk * (dv + 1) : 0;
 }
 
 TI_API int ti_linear_scan(float* y, float* state, long long slot_stride, const void* q, int ld_q, int q_off, const void* k,
                           int ld_k, int k_off, const void* v, int ld_v, int v_off, const float* gate, int ld_gate,
                           int gate_off, int gate_mode, int gate_per_channel, float tau, const float* a_log,
                           const float* dt_bias, const float* skip, float q_scale, const int* cu_seqlens,
-                          const int* state_slots, int num_seqs, int heads, int groups, int dk, int dv, int dtype,
-                          cudaStream_t stream) {
+                          const int* state_slots, int num_seqs, int heads, int groups, int dk, int dv, int stretches,
+                          float* scratch, long long scratch_floats, int dtype, cudaStream_t stream) {
     TI_REQUIRE(num_seqs >= 0 && heads > 0 && groups > 0 && heads % groups == 0 && dk > 0 && dv > 0, "linear_scan: bad sizes");
     TI_REQUIRE(dk <= 1024, "linear_scan: %d key channels a head (at most 1024)", dk);
     TI_REQUIRE(gate_mode >= 0 && gate_mode <= 2 && gate, "linear_scan: unknown gate %d", gate_mode);
     TI_REQUIRE(gate_mode != LS_GATE_STEP || (a_log && !gate_per_channel), "linear_scan: the step-size gate is one number a head and needs A_log");
     TI_REQUIRE(gate_mode != LS_GATE_SIGMOID_POW || tau > 0.f, "linear_scan: tau must be positive");
     TI_REQUIRE(num_seqs <= 65535, "linear_scan: too many requests");
+    TI_REQUIRE(stretches >= 1 && stretches <= 1024, "linear_scan: %d stretches", stretches);
+    TI_REQUIRE(stretches == 1 || (scratch && scratch_floats >= ti_linear_scan_scratch_floats(num_seqs, heads, dk, dv, stretches)),
+               "linear_scan: %d stretches need %lld floats of scratch", stretches,
+               ti_linear_scan_scratch_floats(num_seqs, heads, dk, dv, stretches));
     if (num_seqs == 0) return 0;
     // rows of a column over KP lanes, KPT rows a lane: the fewest lanes that keep a lane's share at 16 rows or fewer
     int kp = 1;
@@ -155,21 +217,38 @@ TI_API int ti_linear_scan(float* y, float* state, long long slot_stride, const v
     const size_t smem = (size_t)chunk * (3 * dkp + cols_per_block) * sizeof(float);
     LinearScanArgs a = {y, state, slot_stride, q, k, v, ld_q, q_off, ld_k, k_off, ld_v, v_off, gate, ld_gate, gate_off,
                         gate_mode, gate_per_channel, tau, a_log, dt_bias, skip, q_scale, cu_seqlens, state_slots,
-                        heads, groups, dk, dv, kp, chunk};
-    dim3 grid(heads * ((dv + cols_per_block - 1) / cols_per_block), num_seqs);
+                        heads, groups, dk, dv, kp, chunk, stretches, scratch,
+                        scratch ? scratch + (long long)num_seqs * stretches * heads * dk * dv : nullptr};
+    dim3 grid(heads * ((dv + cols_per_block - 1) / cols_per_block), num_seqs, stretches);
     typedef __nv_bfloat16 B;
-#define TI_SCAN(KPT)                                                                                          \
-    do {                                                                                                      \
-        if (dtype == TI_F32) ti_launch(linear_scan_kernel<float, KPT>, grid, LS_WARPS * 32, smem, stream, a); \
-        else ti_launch(linear_scan_kernel<B, KPT>, grid, LS_WARPS * 32, smem, stream, a);                     \
+#define TI_SCAN(KPT, MODE)                                                                                          \
+    do {                                                                                                            \
+        if (dtype == TI_F32) ti_launch(linear_scan_kernel<float, KPT, MODE>, grid, LS_WARPS * 32, smem, stream, a); \
+        else ti_launch(linear_scan_kernel<B, KPT, MODE>, grid, LS_WARPS * 32, smem, stream, a);                     \
+    } while (0)
+#define TI_SCAN_PASS(MODE)             \
+    do {                               \
+        if (kpt == 4) TI_SCAN(4, MODE);        \
+        else if (kpt == 8) TI_SCAN(8, MODE);   \
+        else if (kpt == 16) TI_SCAN(16, MODE); \
+        else TI_SCAN(32, MODE);                \
     } while (0)
     TI_REQUIRE(dtype == TI_F32 || dtype == TI_BF16, "linear_scan: unknown dtype %d", dtype);
-    if (kpt == 4) TI_SCAN(4);
-    else if (kpt == 8) TI_SCAN(8);
-    else if (kpt == 16) TI_SCAN(16);
-    else TI_SCAN(32);
+    if (stretches == 1) {
+        TI_SCAN_PASS(0);
+        TI_CHECK_LAUNCH("linear_scan");
+        return 0;
+    }
+    TI_SCAN_PASS(1);
+    TI_CHECK_LAUNCH("linear_scan (stretches from zero)");
+    const int per = heads * dv * dk;
+    ti_launch(linear_scan_fold_kernel, dim3((per + 255) / 256, num_seqs), 256, 0, stream, state, slot_stride, a.part_b,
+              (const float*)a.part_a, state_slots, stretches, heads, dk, dv);
+    TI_CHECK_LAUNCH("linear_scan (fold)");
+    TI_SCAN_PASS(2);
+    TI_CHECK_LAUNCH("linear_scan (stretches from their starts)");
+#undef TI_SCAN_PASS
 #undef TI_SCAN
-    TI_CHECK_LAUNCH("linear_scan");
     return 0;
 }
 

@@ -89,17 +89,18 @@ _SIGNATURES = {
         "ti_gelu": [c_void_p, c_void_p, c_ll, c_int, c_int, c_void_p],
         "ti_scale": [c_void_p, c_ll, c_float, c_void_p],
         "ti_short_conv": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                          c_int, c_int, c_int, c_int, c_int, c_void_p],
+                          c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "ti_conv_state_update": [c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                  c_void_p],
         "ti_conv_qkv_append": [c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_void_p, c_int, c_float, c_int, c_void_p,
                                c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                               c_void_p, c_int, c_void_p],
+                               c_int, c_int, c_void_p, c_int, c_void_p],
         "ti_attention_rows": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                              c_int, c_int, c_int, c_float, c_int, c_int, c_float, c_float, c_void_p, c_int, c_void_p],
+                              c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_float, c_float, c_void_p, c_int, c_void_p],
         "ti_linear_scan": [c_void_p, c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
                            c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_float, c_void_p,
-                           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_ll, c_int, c_void_p],
+        "ti_linear_scan_scratch_floats": [c_int, c_int, c_int, c_int, c_int],
         "ti_gated_group_norm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float,
                                 c_int, c_float, c_int, c_void_p],
     },
@@ -129,6 +130,15 @@ def set_pair_form(allowed: bool) -> None:
 _SIGNATURES["sm100"]["ti_attention_decode_bf16"] = [
     c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
     c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p]
+_SIGNATURES["sm100"]["ti_attention_decode_sink_bf16"] = [
+    c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+    c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p]
+_SIGNATURES["sm100"]["ti_attention_prefill_pair_sink_bf16"] = [
+    c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+    c_float, c_int, c_int, c_float, c_float, c_void_p, c_void_p]
+_SIGNATURES["sm100"]["ti_attention_prefill_tc_sink_bf16"] = [
+    c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+    c_float, c_int, c_int, c_int, c_int, c_void_p, c_ll, c_int, c_float, c_float, c_void_p, c_void_p]
 _SIGNATURES["sm100"]["ti_attention_decode_scratch_floats"] = [c_int, c_int, c_int, c_int, c_int, c_int]
 _SIGNATURES["sm100"]["ti_attention_prefill_pair_bf16"] = [
     c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -608,9 +618,12 @@ def release_scratch(device) -> None:
 def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, *, positions: torch.Tensor,
                     token_seq: torch.Tensor, block_table: torch.Tensor, scale: float,
                     window: Optional[int] = None, step=None,
-                    status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    status: Optional[torch.Tensor] = None, sink: Optional[float] = None,
+                    out_scale: float = 1.0) -> torch.Tensor:
     """Causal attention of q [T, Hq, D] over the pages of each token's own request.
     Token t sees keys max(0, pos - window + 1) .. pos of request ``token_seq[t]``.
+    ``sink``: a logit whose exponential joins every softmax denominator without a value (0.0 adds one to the sum
+    of exp(score)); ``out_scale``: a factor on the output before its rounding.
     Returns [T, Hq * D]. ``step`` (the StepContext of the batch) carries the split of the batch
     into decoded tokens and prompt portions; without it the split is derived here (a device read)."""
     _check(q, "q", None, 3)
@@ -625,9 +638,13 @@ def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, *, positions: torch
     out = torch.empty((t, hq * d), dtype=q.dtype, device=q.device)
     if t == 0:
         return out
+    has_sink, sink_v = int(sink is not None), float(sink or 0.0)
     if not attention_tensor_cores_ok(q, kv_cache):
         if q.dtype == torch.bfloat16:
             _warn_generic_attention(hq, hkv, d, page_size)
+        if has_sink or out_scale != 1.0:
+            return attention_rows(q, kv_cache, v_dim=d, positions=positions, token_seq=token_seq, block_table=block_table,
+                                  scale=scale, sink=sink, window=window, out_scale=out_scale, status=status)
         _run("core", "ti_attention_generic", out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(),
              positions.data_ptr(), token_seq.data_ptr(), block_table.data_ptr(), block_table.shape[1],
              t, hq, hkv, d, page_size, num_pages, float(scale), int(window or 0), _ptr(status),
@@ -660,10 +677,11 @@ def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, *, positions: torch
     kstatus = kernel_status(q.device).data_ptr()
     if num_decode:
         scratch = _decode_scratch(q.device, decode_scratch_floats(num_decode, hq, hkv, d, max_context, int(window or 0)))
-        _run("sm100", "ti_attention_decode_bf16", out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(),
+        _run("sm100", "ti_attention_decode_sink_bf16", out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(),
              scratch.data_ptr(), scratch.numel(), decode_rows.data_ptr(), num_decode, positions.data_ptr(),
              token_seq.data_ptr(), block_table.data_ptr(), block_table.shape[1], hq, hkv, d, page_size,
-             num_pages, float(scale), int(window or 0), int(max_context), kstatus, _stream())
+             num_pages, float(scale), int(window or 0), int(max_context), has_sink, sink_v, float(out_scale), kstatus,
+             _stream())
     def one_tile_kernel(first: int, count: int, halves: int) -> None:
         # Few query tiles behind a long prefix: the keys are shared out over CTAs too (at least 1,024 to a CTA),
         # so that most SMs have a CTA; their partial results meet in a merge kernel.
@@ -676,15 +694,15 @@ def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, *, positions: torch
         if splits > 1:
             scratch = _decode_scratch(q.device, count * (2 if halves else 1) * splits * hq * 128 * (d + 2))
             scratch_ptr, scratch_floats = scratch.data_ptr(), scratch.numel()
-        _run("sm100", "ti_attention_prefill_tc_bf16", out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(),
+        _run("sm100", "ti_attention_prefill_tc_sink_bf16", out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(),
              tiles.data_ptr() + 16 * first, count, t, block_table.data_ptr(), block_table.shape[1], hq, hkv, d, page_size,
-             num_pages, float(scale), int(window or 0), halves, splits, split_keys, scratch_ptr, scratch_floats, kstatus,
-             _stream())
+             num_pages, float(scale), int(window or 0), halves, splits, split_keys, scratch_ptr, scratch_floats, has_sink,
+             sink_v, float(out_scale), kstatus, _stream())
 
     if num_pairs * hq >= PAIR_MIN_CTAS:             # two query tiles a CTA
-        _run("sm100", "ti_attention_prefill_pair_bf16", out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(),
+        _run("sm100", "ti_attention_prefill_pair_sink_bf16", out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(),
              tiles.data_ptr(), num_pairs, t, block_table.data_ptr(), block_table.shape[1], hq, hkv, d, page_size,
-             num_pages, float(scale), int(window or 0), kstatus, _stream())
+             num_pages, float(scale), int(window or 0), has_sink, sink_v, float(out_scale), kstatus, _stream())
     elif num_pairs:                                 # too few of them to fill the machine: one query tile a CTA
         one_tile_kernel(0, num_pairs, 1)
     if num_tiles > num_pairs:                       # ends of portions of at most 128 rows
@@ -1136,10 +1154,11 @@ def _slot_stride(state: torch.Tensor, inner: int, name: str) -> int:
 
 def short_conv(x: torch.Tensor, *, offset: int, width: int, history: torch.Tensor, weight: torch.Tensor,
                bias: Optional[torch.Tensor], silu: bool, token_seq: torch.Tensor, cu_seqlens: torch.Tensor,
-               state_slots: torch.Tensor) -> torch.Tensor:
+               state_slots: torch.Tensor, shift_history: bool = False) -> torch.Tensor:
     """Causal per-channel convolution over time of columns [offset, offset + width) of ``x`` [T, row], ``weight``
     float32 [width, taps] (last column: the current token), then + bias and silu if asked. Inputs of earlier steps
-    come from ``history`` float32 [slots, taps - 1, width] (oldest first), which ``conv_state_update`` keeps."""
+    come from ``history`` float32 [slots, taps - 1, width] (oldest first), which ``conv_state_update`` keeps; in a
+    step in which EVERY request brings one token, ``shift_history`` lets this kernel move the histories on itself."""
     _check(x, "x", None, 2)
     _check(weight, "weight", torch.float32, 2)
     taps = weight.shape[1]
@@ -1151,7 +1170,7 @@ def short_conv(x: torch.Tensor, *, offset: int, width: int, history: torch.Tenso
     out = torch.empty((x.shape[0], width), dtype=x.dtype, device=x.device)
     _run("hybrid", "ti_short_conv", out.data_ptr(), x.data_ptr(), x.shape[1], offset, history.data_ptr() if taps > 1 else None,
          stride, weight.data_ptr(), _ptr(bias), token_seq.data_ptr(), cu_seqlens.data_ptr(), state_slots.data_ptr(),
-         x.shape[0], width, taps, int(silu), _dtype_code(x), _stream())
+         x.shape[0], width, taps, int(silu), int(shift_history), _dtype_code(x), _stream())
     return out
 
 
@@ -1167,16 +1186,29 @@ def conv_state_update(history: torch.Tensor, x: torch.Tensor, *, offset: int, wi
          cu_seqlens.data_ptr(), state_slots.data_ptr(), num_seqs, width, taps, _dtype_code(x), _stream())
 
 
+def _kv_planes(cache: torch.Tensor, num_kv_heads: int, head_dim: int, v_dim: int) -> int:
+    """1 for a cache of rows [k | v], [1, pages, Hkv, page, d + dv]; 2 for planes [2, pages, Hkv, page, d] (d == dv)."""
+    if cache.shape[2] == num_kv_heads:
+        if cache.shape[0] == 1 and cache.shape[4] == head_dim + v_dim:
+            return 1
+        if cache.shape[0] == 2 and cache.shape[4] == head_dim == v_dim:
+            return 2
+    raise KernelError(f"cache shape {tuple(cache.shape)} is neither [1, pages, {num_kv_heads}, page, {head_dim + v_dim}] "
+                      f"nor, for keys and values of one size, [2, pages, {num_kv_heads}, page, {head_dim}]")
+
+
 def conv_qkv_append(qkv: torch.Tensor, *, num_heads: int, num_kv_heads: int, head_dim: int, v_dim: int,
                     conv_weight: Optional[torch.Tensor], history: Optional[torch.Tensor],
                     temperature: Optional[tuple], positions: torch.Tensor, token_seq: torch.Tensor,
                     cu_seqlens: torch.Tensor, state_slots: torch.Tensor, cache: Optional[torch.Tensor],
-                    block_table: torch.Tensor, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    block_table: torch.Tensor, status: Optional[torch.Tensor] = None,
+                    shift_history: bool = False) -> torch.Tensor:
     """``qkv`` [T, Hq d + Hkv (d + dv)] packed [q | k | v]: a short causal convolution per channel
     (``conv_weight`` float32 [channels, taps] with ``history`` float32 [slots, taps - 1, channels]; None: none),
     then q times its position's temperature 1 + coef * ln(floor((p + 1) / every) + 1) (``temperature`` =
     (coef, every) or None). Returns q [T, Hq, d]; k and v go to the token's row [k | v] of ``cache``
-    [1, pages, Hkv, page, d + dv]."""
+    [1, pages, Hkv, page, d + dv], or, where d == dv, to the planes of a cache [2, pages, Hkv, page, d].
+    ``shift_history``: as in ``short_conv``."""
     _check(qkv, "qkv", None, 2)
     t = qkv.shape[0]
     width = num_heads * head_dim + num_kv_heads * (head_dim + v_dim)
@@ -1192,18 +1224,17 @@ def conv_qkv_append(qkv: torch.Tensor, *, num_heads: int, num_kv_heads: int, hea
             stride = _slot_stride(history, (taps - 1) * width, "history")
     _check(positions, "positions", torch.int32, 1)
     _check(block_table, "block_table", torch.int32, 2)
-    page_size = num_pages = 1
+    page_size = num_pages = planes = 1
     if cache is not None:
         _check(cache, "cache", qkv.dtype, 5)
-        if cache.shape[0] != 1 or cache.shape[2] != num_kv_heads or cache.shape[4] != head_dim + v_dim:
-            raise KernelError(f"cache shape {tuple(cache.shape)} is not [1, pages, Hkv, page, d + dv]")
+        planes = _kv_planes(cache, num_kv_heads, head_dim, v_dim)
         num_pages, page_size = cache.shape[1], cache.shape[3]
     coef, every = (float(temperature[0]), int(temperature[1])) if temperature else (0.0, 0)
     q = torch.empty((t, num_heads, head_dim), dtype=qkv.dtype, device=qkv.device)
     _run("hybrid", "ti_conv_qkv_append", q.data_ptr(), _ptr(cache), qkv.data_ptr(), history.data_ptr() if taps > 1 else None,
          stride, _ptr(conv_weight), taps, coef, every, positions.data_ptr(), token_seq.data_ptr(), cu_seqlens.data_ptr(),
          state_slots.data_ptr(), block_table.data_ptr(), block_table.shape[1], t, num_heads, num_kv_heads, head_dim, v_dim,
-         page_size, num_pages, _ptr(status), _dtype_code(qkv), _stream())
+         page_size, num_pages, planes, int(shift_history), _ptr(status), _dtype_code(qkv), _stream())
     return q
 
 
@@ -1211,7 +1242,7 @@ def attention_rows(q: torch.Tensor, cache: torch.Tensor, *, v_dim: int, position
                    block_table: torch.Tensor, scale: float, sink: Optional[float] = None, window: Optional[int] = None,
                    out_scale: float = 1.0, step=None, status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of q [T, Hq, d] over pages whose rows are [k (d) | v (dv)] (``cache``
-    [1, pages, Hkv, page, d + dv]). ``sink``: a logit whose exponential joins every softmax denominator without a
+    [1, pages, Hkv, page, d + dv]; or planes [2, pages, Hkv, page, d] where d == dv), float32 arithmetic, any sizes. ``sink``: a logit whose exponential joins every softmax denominator without a
     value (0.0: one is added to the sum of exp(score)). Returns [T, Hq * dv], multiplied by ``out_scale`` before
     its rounding."""
     _check(q, "q", None, 3)
@@ -1220,15 +1251,14 @@ def attention_rows(q: torch.Tensor, cache: torch.Tensor, *, v_dim: int, position
     _check(token_seq, "token_seq", torch.int32, 1)
     _check(block_table, "block_table", torch.int32, 2)
     t, hq, d = q.shape
-    _, num_pages, hkv, page_size, row = cache.shape
-    if cache.shape[0] != 1 or row != d + v_dim:
-        raise KernelError("attention_rows: the cache's rows are not [k | v] of these sizes")
+    _, num_pages, hkv, page_size, _row = cache.shape
+    planes = _kv_planes(cache, hkv, d, v_dim)
     out = torch.empty((t, hq * v_dim), dtype=q.dtype, device=q.device)
     if t == 0:
         return out
     _run("hybrid", "ti_attention_rows", out.data_ptr(), q.data_ptr(), cache.data_ptr(), positions.data_ptr(),
          token_seq.data_ptr(), block_table.data_ptr(), block_table.shape[1], t, hq, hkv, d, v_dim, page_size, num_pages,
-         float(scale), int(window or 0), int(sink is not None), float(sink or 0.0), float(out_scale), _ptr(status),
+         planes, float(scale), int(window or 0), int(sink is not None), float(sink or 0.0), float(out_scale), _ptr(status),
          _dtype_code(q), _stream())
     return out
 
@@ -1249,14 +1279,32 @@ class ScanGate:
         self.tau, self.a_log, self.dt_bias = tau, a_log, dt_bias
 
 
+SCAN_MIN_STRETCH = 32        # tokens a stretch of a long portion has at least
+SCAN_TARGET_BLOCKS = 148 * 8
+
+
+def scan_stretches(max_q_len: int, num_seqs: int, heads: int, key_dim: int, value_dim: int) -> int:
+    """Into how many stretches ``linear_scan`` cuts the requests' tokens: enough to have several blocks on every SM,
+    none shorter than SCAN_MIN_STRETCH tokens; 1 for steps of short portions and decoded tokens."""
+    if max_q_len < 2 * SCAN_MIN_STRETCH:
+        return 1
+    lanes = 1
+    while lanes < 32 and -(-key_dim // lanes) > 16:
+        lanes *= 2
+    blocks = num_seqs * heads * -(-value_dim // (4 * (32 // lanes)))
+    return max(1, min(-(-SCAN_TARGET_BLOCKS // blocks), max_q_len // SCAN_MIN_STRETCH, 64))
+
+
 def linear_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: ScanGate, *, state: torch.Tensor, heads: int,
                 groups: int, key_dim: int, value_dim: int, q_offset: int = 0, k_offset: int = 0, v_offset: int = 0,
                 q_scale: float = 1.0, skip: Optional[torch.Tensor] = None, cu_seqlens: torch.Tensor,
-                state_slots: torch.Tensor, num_seqs: int) -> torch.Tensor:
+                state_slots: torch.Tensor, num_seqs: int, max_q_len: int = 0) -> torch.Tensor:
     """Per request and head, over the step's tokens in order: S <- diag(a) S + k v^T, o = S^T (q * q_scale)
     (+ skip[h] * v), from and back into ``state`` float32 [slots, heads, value_dim, key_dim] (S transposed).
     q and k: columns [offset, + groups * key_dim) of their tensors (head h reads group h // (heads / groups));
-    v: columns [offset, + heads * value_dim). Returns o float32 [T, heads * value_dim]."""
+    v: columns [offset, + heads * value_dim). Returns o float32 [T, heads * value_dim]. ``max_q_len`` (a host
+    number: the most tokens a request brings, 0: unknown) only decides into how many stretches long portions are cut
+    to run side by side."""
     for name, ten in (("q", q), ("k", k), ("v", v)):
         _check(ten, name, q.dtype, 2)
     _check(gate.values, "gate", torch.float32, 2)
@@ -1276,11 +1324,17 @@ def linear_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: ScanGat
     out = torch.empty((t, heads * value_dim), dtype=torch.float32, device=q.device)
     if t == 0:
         return out
+    stretches, scratch = scan_stretches(max_q_len or t, num_seqs, heads, key_dim, value_dim), None
+    if stretches > 1:
+        fn = _fn("hybrid", "ti_linear_scan_scratch_floats")
+        fn.restype = ctypes.c_longlong
+        scratch = torch.empty(int(fn(num_seqs, heads, key_dim, value_dim, stretches)), dtype=torch.float32, device=q.device)
     _run("hybrid", "ti_linear_scan", out.data_ptr(), state.data_ptr(), stride, q.data_ptr(), q.shape[1], q_offset,
          k.data_ptr(), k.shape[1], k_offset, v.data_ptr(), v.shape[1], v_offset, gate.values.data_ptr(),
          gate.values.shape[1], gate.offset, ScanGate.KINDS[gate.kind], int(gate.per_channel), float(gate.tau),
          _ptr(gate.a_log), _ptr(gate.dt_bias), _ptr(skip), float(q_scale), cu_seqlens.data_ptr(), state_slots.data_ptr(),
-         num_seqs, heads, groups, key_dim, value_dim, _dtype_code(q), _stream())
+         num_seqs, heads, groups, key_dim, value_dim, stretches, _ptr(scratch), scratch.numel() if scratch is not None else 0,
+         _dtype_code(q), _stream())
     return out
 
 

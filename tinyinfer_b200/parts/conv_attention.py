@@ -1,7 +1,7 @@
 """Grouped-query softmax attention whose q, k and v pass a short causal convolution over time, without a rotation:
 packed projection [q | k | v] with biases, the convolution per channel (its last taps - 1 inputs per request live
 in the request's state slot), a query temperature that grows with the logarithm of the position, scores
-(q . k) * scale over the request's cached rows [k | v] (keys and values may differ in size), a softmax whose
+(q . k) * scale over the request's cached keys and values (which may differ in size), a softmax whose
 denominator may hold one more term exp(sink) without a value, and the output projection.
 
 Convolution, temperature, scores and softmax are float32; q and the cached rows are rounded once.
@@ -32,7 +32,11 @@ class ConvAttention(Mixer):
         return s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim, s.num_kv_heads * s.v_dim
 
     def cache_need(self):
+        """Keys and values of one size lie in two planes, which is what the tensor-core attention kernels read;
+        of different sizes, side by side in one row per token."""
         s = self.spec
+        if s.head_dim == s.v_dim:
+            return CacheNeed(s.num_kv_heads, s.head_dim, s.window, planes=2)
         return CacheNeed(s.num_kv_heads, s.head_dim + s.v_dim, s.window, planes=1)
 
     def state_need(self):
@@ -68,14 +72,20 @@ class ConvAttention(Mixer):
         width = sum(self._sizes)
         qkv = ops.linear(x, self.w_qkv, bias=self.b_qkv)
         history = cache.state.unflatten(1, (s.conv_taps - 1, width)) if s.conv_taps > 1 else None
+        single = step.num_tokens == step.num_seqs          # every request brings one token: the kernel keeps the history itself
         q = ops.conv_qkv_append(
             qkv, num_heads=s.num_heads, num_kv_heads=s.num_kv_heads, head_dim=s.head_dim, v_dim=s.v_dim,
             conv_weight=self.conv_w, history=history, temperature=s.query_temperature, positions=step.positions,
             token_seq=step.token_seq, cu_seqlens=step.cu_seqlens, state_slots=step.state_slots,
-            cache=cache.kv if cache.writes else None, block_table=cache.block_table, status=step.status)
-        if history is not None and cache.writes:
+            cache=cache.kv if cache.writes else None, block_table=cache.block_table, status=step.status,
+            shift_history=single and cache.writes)
+        if history is not None and cache.writes and not single:
             ops.conv_state_update(history, qkv, offset=0, width=width, taps=s.conv_taps, cu_seqlens=step.cu_seqlens,
                                   state_slots=step.state_slots, num_seqs=step.num_seqs)
+        if cache.kv.shape[0] == 2:          # the paged attention of the plain decoder, tensor cores where the sizes allow
+            return ops.paged_attention(q, cache.kv, positions=step.positions, token_seq=step.token_seq,
+                                       block_table=cache.block_table, scale=s.scale, window=s.window, step=step,
+                                       status=step.status, sink=s.sink, out_scale=out_scale)
         return ops.attention_rows(q, cache.kv, v_dim=s.v_dim, positions=step.positions, token_seq=step.token_seq,
                                   block_table=cache.block_table, scale=s.scale, sink=s.sink, window=s.window,
                                   out_scale=out_scale, step=step, status=step.status)

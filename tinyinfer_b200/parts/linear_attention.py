@@ -53,7 +53,7 @@ class GatedLinearAttention(Mixer):
         o = ops.linear_scan(packed, packed, packed, ops.ScanGate("sigmoid_power", logits, per_channel=True, tau=s.tau),
                             state=state, heads=s.num_heads, groups=s.num_heads, key_dim=s.key_dim, value_dim=s.value_dim,
                             q_offset=0, k_offset=nk, v_offset=2 * nk, q_scale=s.key_dim ** -0.5,
-                            cu_seqlens=step.cu_seqlens, state_slots=step.state_slots, num_seqs=step.num_seqs)
+                            cu_seqlens=step.cu_seqlens, state_slots=step.state_slots, num_seqs=step.num_seqs, max_q_len=step.max_q_len)
         return ops.gated_group_norm(o, packed, self.norm_w, group=s.value_dim, eps=s.norm_eps, gate_first=False,
                                     out_dtype=self.dtype, gate_offset=2 * nk + nv, out_scale=out_scale)
 

@@ -62,15 +62,17 @@ class StateSpace(Mixer):
         main = ops.linear(x, self.w_main)
         dt = ops.linear(x, self.w_dt, out_float32=True)                              # float32 [T, heads]
         state, history = (state_slices(cache.state, self._state_shapes()) + [None])[:2]
+        single = step.num_tokens == step.num_seqs          # every request brings one token: the kernel keeps the history itself
         xbc = ops.short_conv(main, offset=inner, width=s.conv_size, history=history, weight=self.conv_w,
                              bias=self.conv_b, silu=True, token_seq=step.token_seq, cu_seqlens=step.cu_seqlens,
-                             state_slots=step.state_slots)
-        ops.conv_state_update(history, main, offset=inner, width=s.conv_size, taps=s.conv_taps,
-                              cu_seqlens=step.cu_seqlens, state_slots=step.state_slots, num_seqs=step.num_seqs)
+                             state_slots=step.state_slots, shift_history=single)
+        if not single:
+            ops.conv_state_update(history, main, offset=inner, width=s.conv_size, taps=s.conv_taps,
+                                  cu_seqlens=step.cu_seqlens, state_slots=step.state_slots, num_seqs=step.num_seqs)
         gate = ops.ScanGate("step_size", dt, per_channel=False, a_log=self.a_log, dt_bias=self.dt_bias)
         y = ops.linear_scan(xbc, xbc, xbc, gate, state=state, heads=s.num_heads, groups=s.groups, key_dim=s.state_dim,
                             value_dim=s.head_dim, q_offset=inner + gn, k_offset=inner, v_offset=0, skip=self.skip,
-                            cu_seqlens=step.cu_seqlens, state_slots=step.state_slots, num_seqs=step.num_seqs)
+                            cu_seqlens=step.cu_seqlens, state_slots=step.state_slots, num_seqs=step.num_seqs, max_q_len=step.max_q_len)
         return ops.gated_group_norm(y, main, self.norm_w, group=inner // s.norm_groups, eps=s.norm_eps, gate_first=True,
                                     out_dtype=self.dtype, gate_offset=0, out_scale=out_scale)
 
