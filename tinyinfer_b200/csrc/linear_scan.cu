@@ -7,12 +7,16 @@
 //   gate 1 (sigmoid power) a = sigmoid(gate)^(1 / tau) = exp(logsigmoid(gate) / tau), per key channel
 //   gate 2 (step size)     dt = softplus(gate + dt_bias[h]), a = exp(-exp(A_log[h]) * dt) per head, and k_t is
 //                          multiplied by dt (a discretised state-space model: "Transformers are SSMs", Dao and Gu, 2024)
+// A small kernel makes the decays (and the keys' factors) of a step once, float32 [T][H * dk] or [T][H]; the scan reads
+// them like any other operand, so none of its blocks repeats a logarithm or an exponential.
 // Decays, their logarithms, softplus, exponentials, the state and the outputs are float32; q, k and v are read in
 // the compute dtype from wherever they lie (row length and first column given), several heads may share one
 // group of q and k.
 //
-// A block is one request x one head x a few columns of S; a thread holds KPT rows of one column, the rows of a
-// column are spread over KP lanes (row = r * KP + lane part), whose partial sums of o meet by shuffles. The step's
+// A block is one request x one head x a few columns of S; a thread holds KPT neighbouring rows of one column, the rows
+// of a column are spread over KP lanes (row = lane part * KPT + r), whose partial sums of o meet by shuffles; a thread
+// reads its rows of q, k and the decay from shared memory four at a time (the parts lie KPT + 4 floats apart, so the
+// lanes' 16-byte reads fall into different banks). The step's
 // tokens of the request are walked in order; q, k and the decays of a few tokens at a time are staged in shared
 // memory by the whole block.
 //
@@ -38,10 +42,10 @@ struct LinearScanArgs {
     long long slot_stride;
     const void *q, *k, *v;    // rows of ld_* elements, first column *_off; q and k: [groups][dk], v: [H][dv]
     int ld_q, q_off, ld_k, k_off, ld_v, v_off;
-    const float* gate;        // float32 rows of ld_gate, first column gate_off
-    int ld_gate, gate_off, gate_mode, gate_per_channel;
-    float tau;
-    const float *a_log, *dt_bias, *skip;      // [H] each, or null
+    const float* decay;       // float32 rows of ld_decay, first column decay_off: [H][dk] (per channel) or [H]
+    int ld_decay, decay_off, per_channel;
+    const float* kscale;      // float32 [T][H] or null: a factor on the keys of a head
+    const float* skip;        // [H] or null
     float q_scale;
     const int *cu_seqlens, *state_slots;
     int heads, groups, dk, dv, kp, chunk;
@@ -57,6 +61,8 @@ __global__ void __launch_bounds__(LS_WARPS * 32) linear_scan_kernel(LinearScanAr
     ti_grid_launch_dependents();
     ti_grid_wait();
     const int KP = a.kp, dkp = KP * KPT;                 // dk rounded up to what the lanes hold
+    constexpr int PITCH = KPT + 4;                       // floats from one lane part's rows to the next in shared memory
+    const int trow = KP * PITCH;                         // floats a token takes in each of sq, sk, sa
     const int cols_per_warp = 32 / KP, cols_per_block = LS_WARPS * cols_per_warp;
     const int col_blocks = (a.dv + cols_per_block - 1) / cols_per_block;
     const int h = blockIdx.x / col_blocks, cb = blockIdx.x % col_blocks;
@@ -73,10 +79,10 @@ __global__ void __launch_bounds__(LS_WARPS * 32) linear_scan_kernel(LinearScanAr
         row1 = row0 + min(n, ((int)blockIdx.z + 1) * len);
         row0 = first;
     }
-    float* sq = smem;                                    // [chunk][dkp]
-    float* sk = sq + (size_t)a.chunk * dkp;
-    float* sa = sk + (size_t)a.chunk * dkp;
-    float* sv = sa + (size_t)a.chunk * dkp;              // [chunk][cols_per_block]
+    float* sq = smem;                                    // [chunk][KP][PITCH]
+    float* sk = sq + (size_t)a.chunk * trow;
+    float* sa = sk + (size_t)a.chunk * trow;
+    float* sv = sa + (size_t)a.chunk * trow;             // [chunk][cols_per_block]
     const T* q = (const T*)a.q;
     const T* k = (const T*)a.k;
     const T* v = (const T*)a.v;
@@ -87,17 +93,11 @@ __global__ void __launch_bounds__(LS_WARPS * 32) linear_scan_kernel(LinearScanAr
     float S[KPT], A[MODE == 1 ? KPT : 1];
 #pragma unroll
     for (int r = 0; r < KPT; ++r) {
-        const int idx = r * KP + kpart;
+        const int idx = kpart * KPT + r;
         S[r] = (MODE != 1 && col_ok && idx < a.dk) ? srow[idx] : 0.f;
         if (MODE == 1) A[r] = 1.f;
     }
     const float skip = a.skip ? a.skip[h] : 0.f;
-    float rate = 0.f, bias = 0.f;
-    if (a.gate_mode == LS_GATE_STEP) {
-        rate = expf(a.a_log[h]);
-        bias = a.dt_bias ? a.dt_bias[h] : 0.f;
-    }
-    const float inv_tau = a.gate_mode == LS_GATE_SIGMOID_POW ? 1.f / a.tau : 0.f;
 
     for (int t0 = row0; t0 < row1; t0 += a.chunk) {
         const int n = min(a.chunk, row1 - t0);
@@ -108,18 +108,13 @@ __global__ void __launch_bounds__(LS_WARPS * 32) linear_scan_kernel(LinearScanAr
             if (idx < a.dk) {
                 qv = to_f32(q[(size_t)t * a.ld_q + a.q_off + g * a.dk + idx]) * a.q_scale;
                 kv = to_f32(k[(size_t)t * a.ld_k + a.k_off + g * a.dk + idx]);
-                const float gv = a.gate[(size_t)t * a.ld_gate + a.gate_off + (a.gate_per_channel ? h * a.dk + idx : h)];
-                if (a.gate_mode == LS_GATE_RAW) av = gv;
-                else if (a.gate_mode == LS_GATE_SIGMOID_POW) av = expf(ls_logsigmoid(gv) * inv_tau);
-                else {
-                    const float dt = ls_softplus(gv + bias);
-                    av = expf(-rate * dt);
-                    kv *= dt;
-                }
+                if (a.kscale) kv *= a.kscale[(size_t)t * a.heads + h];
+                av = a.decay[(size_t)t * a.ld_decay + a.decay_off + (a.per_channel ? h * a.dk + idx : h)];
             }
-            sq[e] = qv;
-            sk[e] = kv;
-            sa[e] = av;
+            const int at = tt * trow + (idx / KPT) * PITCH + idx % KPT;
+            sq[at] = qv;
+            sk[at] = kv;
+            sa[at] = av;
         }
         for (int e = tid; e < n * cols_per_block; e += LS_WARPS * 32) {
             const int tt = e / cols_per_block, c = cb * cols_per_block + e % cols_per_block;
@@ -128,17 +123,30 @@ __global__ void __launch_bounds__(LS_WARPS * 32) linear_scan_kernel(LinearScanAr
         __syncthreads();
         for (int tt = 0; tt < n; ++tt) {
             const float vv = sv[tt * cols_per_block + warp * cols_per_warp + lane / KP];
-            const float* pq = sq + (size_t)tt * dkp + kpart;
-            const float* pk = sk + (size_t)tt * dkp + kpart;
-            const float* pa = sa + (size_t)tt * dkp + kpart;
-            float o = 0.f;
+            const float4* pq = reinterpret_cast<const float4*>(sq + (size_t)tt * trow + kpart * PITCH);
+            const float4* pk = reinterpret_cast<const float4*>(sk + (size_t)tt * trow + kpart * PITCH);
+            const float4* pa = reinterpret_cast<const float4*>(sa + (size_t)tt * trow + kpart * PITCH);
+            float o = 0.f, o2 = 0.f;
 #pragma unroll
-            for (int r = 0; r < KPT; ++r) {
-                S[r] = fmaf(pa[r * KP], S[r], pk[r * KP] * vv);
-                if (MODE == 1) A[r] *= pa[r * KP];
-                else o = fmaf(S[r], pq[r * KP], o);
+            for (int r4 = 0; r4 < KPT / 4; ++r4) {
+                const float4 av = pa[r4], kv = pk[r4];
+                const float ar[4] = {av.x, av.y, av.z, av.w}, kr[4] = {kv.x, kv.y, kv.z, kv.w};
+                float qr[4] = {0.f, 0.f, 0.f, 0.f};
+                if (MODE != 1) {
+                    const float4 qv = pq[r4];
+                    qr[0] = qv.x; qr[1] = qv.y; qr[2] = qv.z; qr[3] = qv.w;
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int r = r4 * 4 + j;
+                    S[r] = fmaf(ar[j], S[r], kr[j] * vv);
+                    if (MODE == 1) A[r] *= ar[j];
+                    else if (j & 1) o2 = fmaf(S[r], qr[j], o2);
+                    else o = fmaf(S[r], qr[j], o);
+                }
             }
             if (MODE != 1) {
+                o += o2;
                 for (int off = 1; off < KP; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
                 if (kpart == 0 && col_ok) a.y[(size_t)(t0 + tt) * a.heads * a.dv + h * a.dv + col] = fmaf(skip, vv, o);
             }
@@ -148,7 +156,7 @@ __global__ void __launch_bounds__(LS_WARPS * 32) linear_scan_kernel(LinearScanAr
     if (col_ok) {
 #pragma unroll
         for (int r = 0; r < KPT; ++r) {
-            const int idx = r * KP + kpart;
+            const int idx = kpart * KPT + r;
             if (idx < a.dk) srow[idx] = S[r];
         }
     }
@@ -156,7 +164,7 @@ __global__ void __launch_bounds__(LS_WARPS * 32) linear_scan_kernel(LinearScanAr
         float* arow = a.part_a + (((size_t)seq * a.stretches + blockIdx.z) * a.heads + h) * a.dk;
 #pragma unroll
         for (int r = 0; r < KPT; ++r) {
-            const int idx = r * KP + kpart;
+            const int idx = kpart * KPT + r;
             if (idx < a.dk) arow[idx] = A[r];
         }
     }
@@ -175,26 +183,59 @@ __global__ void linear_scan_fold_kernel(float* __restrict__ state, long long slo
     const int idx = e % dk, h = e / (dv * dk);
     float* slot = state + (size_t)state_slots[seq] * slot_stride;
     float S = slot[e];
-    for (int k = 0; k < stretches; ++k) {
-        const size_t part = (size_t)seq * stretches + k;
-        const float b = part_b[part * per + e];
-        const float a = part_a[(part * heads + h) * dk + idx];
-        part_b[part * per + e] = S;
-        S = fmaf(a, S, b);
+    for (int k0 = 0; k0 < stretches; k0 += 8) {          // eight stretches' loads in flight at once
+        float b[8], a[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const size_t part = (size_t)seq * stretches + min(k0 + j, stretches - 1);
+            b[j] = part_b[part * per + e];
+            a[j] = part_a[(part * heads + h) * dk + idx];
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if (k0 + j < stretches) {
+                part_b[((size_t)seq * stretches + k0 + j) * per + e] = S;
+                S = fmaf(a[j], S, b[j]);
+            }
+        }
     }
     slot[e] = S;
+}
+
+// The decays of a step from the model's tensors: one thread per (token, head[, key channel]).
+__global__ void scan_gate_kernel(float* __restrict__ decay, float* __restrict__ kscale, const float* __restrict__ gate,
+                                 int ld_gate, int gate_off, int mode, float inv_tau, const float* __restrict__ a_log,
+                                 const float* __restrict__ dt_bias, int heads, int per_head, size_t n) {
+    ti_grid_launch_dependents();
+    ti_grid_wait();
+    const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= n) return;
+    const size_t t = e / ((size_t)heads * per_head);
+    const int c = (int)(e % ((size_t)heads * per_head)), h = c / per_head;
+    const float gv = gate[t * ld_gate + gate_off + c];
+    if (mode == LS_GATE_SIGMOID_POW) {
+        decay[e] = expf(ls_logsigmoid(gv) * inv_tau);
+    } else {
+        const float dt = ls_softplus(gv + (dt_bias ? dt_bias[h] : 0.f));
+        decay[e] = expf(-expf(a_log[h]) * dt);
+        kscale[e] = dt;
+    }
 }
 
 TI_API long long ti_linear_scan_scratch_floats(int num_seqs, int heads, int dk, int dv, int stretches) {
     return stretches > 1 ? (long long)num_seqs * stretches * heads * dk * (dv + 1) : 0;
 }
 
+// gate_mode 0: `gate` holds the decays themselves. Otherwise they are made first, into `gate_out` (float32, as many
+// entries as the gate has per step: num_tokens x heads (x dk if per channel); gate mode 2 needs as many again behind
+// them for the keys' factors).
 TI_API int ti_linear_scan(float* y, float* state, long long slot_stride, const void* q, int ld_q, int q_off, const void* k,
                           int ld_k, int k_off, const void* v, int ld_v, int v_off, const float* gate, int ld_gate,
                           int gate_off, int gate_mode, int gate_per_channel, float tau, const float* a_log,
                           const float* dt_bias, const float* skip, float q_scale, const int* cu_seqlens,
-                          const int* state_slots, int num_seqs, int heads, int groups, int dk, int dv, int stretches,
-                          float* scratch, long long scratch_floats, int dtype, cudaStream_t stream) {
+                          const int* state_slots, int num_seqs, int num_tokens, int heads, int groups, int dk, int dv,
+                          int stretches, float* scratch, long long scratch_floats, float* gate_out, int dtype,
+                          cudaStream_t stream) {
     TI_REQUIRE(num_seqs >= 0 && heads > 0 && groups > 0 && heads % groups == 0 && dk > 0 && dv > 0, "linear_scan: bad sizes");
     TI_REQUIRE(dk <= 1024, "linear_scan: %d key channels a head (at most 1024)", dk);
     TI_REQUIRE(gate_mode >= 0 && gate_mode <= 2 && gate, "linear_scan: unknown gate %d", gate_mode);
@@ -205,18 +246,33 @@ TI_API int ti_linear_scan(float* y, float* state, long long slot_stride, const v
     TI_REQUIRE(stretches == 1 || (scratch && scratch_floats >= ti_linear_scan_scratch_floats(num_seqs, heads, dk, dv, stretches)),
                "linear_scan: %d stretches need %lld floats of scratch", stretches,
                ti_linear_scan_scratch_floats(num_seqs, heads, dk, dv, stretches));
-    if (num_seqs == 0) return 0;
+    TI_REQUIRE(gate_mode == LS_GATE_RAW || gate_out, "linear_scan: the decays need a place to be made in");
+    if (num_seqs == 0 || num_tokens == 0) return 0;
+    const float* decay = gate;
+    const float* kscale = nullptr;
+    int ld_decay = ld_gate, decay_off = gate_off;
+    if (gate_mode != LS_GATE_RAW) {
+        const int per_head = gate_per_channel ? dk : 1;
+        const size_t n = (size_t)num_tokens * heads * per_head;
+        ti_launch(scan_gate_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, gate_out, gate_out + n, gate, ld_gate, gate_off,
+                  gate_mode, gate_mode == LS_GATE_SIGMOID_POW ? 1.f / tau : 0.f, a_log, dt_bias, heads, per_head, n);
+        TI_CHECK_LAUNCH("linear_scan (decays)");
+        decay = gate_out;
+        ld_decay = heads * per_head;
+        decay_off = 0;
+        if (gate_mode == LS_GATE_STEP) kscale = gate_out + n;
+    }
     // rows of a column over KP lanes, KPT rows a lane: the fewest lanes that keep a lane's share at 16 rows or fewer
     int kp = 1;
     while (kp < 32 && (dk + kp - 1) / kp > 16) kp <<= 1;
     const int per_lane = (dk + kp - 1) / kp;
     const int kpt = per_lane <= 4 ? 4 : per_lane <= 8 ? 8 : per_lane <= 16 ? 16 : 32;
-    const int dkp = kp * kpt, cols_per_block = LS_WARPS * (32 / kp);
-    int chunk = 16;
-    while (chunk > 1 && (size_t)chunk * (3 * dkp + cols_per_block) * sizeof(float) > 40 * 1024) chunk >>= 1;
-    const size_t smem = (size_t)chunk * (3 * dkp + cols_per_block) * sizeof(float);
-    LinearScanArgs a = {y, state, slot_stride, q, k, v, ld_q, q_off, ld_k, k_off, ld_v, v_off, gate, ld_gate, gate_off,
-                        gate_mode, gate_per_channel, tau, a_log, dt_bias, skip, q_scale, cu_seqlens, state_slots,
+    const int trow = kp * (kpt + 4), cols_per_block = LS_WARPS * (32 / kp);     // a token's floats in shared memory, padded
+    int chunk = 16;          // more would be fewer barriers, and fewer blocks an SM (shared memory): measured slower
+    while (chunk > 1 && (size_t)chunk * (3 * trow + cols_per_block) * sizeof(float) > 40 * 1024) chunk >>= 1;
+    const size_t smem = (size_t)chunk * (3 * trow + cols_per_block) * sizeof(float);
+    LinearScanArgs a = {y, state, slot_stride, q, k, v, ld_q, q_off, ld_k, k_off, ld_v, v_off, decay, ld_decay, decay_off,
+                        gate_per_channel, kscale, skip, q_scale, cu_seqlens, state_slots,
                         heads, groups, dk, dv, kp, chunk, stretches, scratch,
                         scratch ? scratch + (long long)num_seqs * stretches * heads * dk * dv : nullptr};
     dim3 grid(heads * ((dv + cols_per_block - 1) / cols_per_block), num_seqs, stretches);

@@ -99,7 +99,7 @@ _SIGNATURES = {
                               c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_float, c_float, c_void_p, c_int, c_void_p],
         "ti_linear_scan": [c_void_p, c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
                            c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_float, c_void_p,
-                           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_ll, c_int, c_void_p],
+                           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_ll, c_void_p, c_int, c_void_p],
         "ti_linear_scan_scratch_floats": [c_int, c_int, c_int, c_int, c_int],
         "ti_gated_group_norm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float,
                                 c_int, c_float, c_int, c_void_p],
@@ -1280,7 +1280,7 @@ class ScanGate:
 
 
 SCAN_MIN_STRETCH = 32        # tokens a stretch of a long portion has at least
-SCAN_TARGET_BLOCKS = 148 * 8
+SCAN_TARGET_BLOCKS = 148 * 7  # what runs side by side at 72 registers a thread: more blocks would wait for a second round
 
 
 def scan_stretches(max_q_len: int, num_seqs: int, heads: int, key_dim: int, value_dim: int) -> int:
@@ -1292,7 +1292,7 @@ def scan_stretches(max_q_len: int, num_seqs: int, heads: int, key_dim: int, valu
     while lanes < 32 and -(-key_dim // lanes) > 16:
         lanes *= 2
     blocks = num_seqs * heads * -(-value_dim // (4 * (32 // lanes)))
-    return max(1, min(-(-SCAN_TARGET_BLOCKS // blocks), max_q_len // SCAN_MIN_STRETCH, 64))
+    return max(1, min(SCAN_TARGET_BLOCKS // blocks, max_q_len // SCAN_MIN_STRETCH, 64))
 
 
 def linear_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: ScanGate, *, state: torch.Tensor, heads: int,
@@ -1329,12 +1329,16 @@ def linear_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: ScanGat
         fn = _fn("hybrid", "ti_linear_scan_scratch_floats")
         fn.restype = ctypes.c_longlong
         scratch = torch.empty(int(fn(num_seqs, heads, key_dim, value_dim, stretches)), dtype=torch.float32, device=q.device)
+    made = None          # the decays (and the keys' factors) as the scan reads them, unless the gate holds them already
+    if gate.kind != "raw":
+        made = torch.empty(t * heads * (key_dim if gate.per_channel else 1) * (2 if gate.kind == "step_size" else 1),
+                           dtype=torch.float32, device=q.device)
     _run("hybrid", "ti_linear_scan", out.data_ptr(), state.data_ptr(), stride, q.data_ptr(), q.shape[1], q_offset,
          k.data_ptr(), k.shape[1], k_offset, v.data_ptr(), v.shape[1], v_offset, gate.values.data_ptr(),
          gate.values.shape[1], gate.offset, ScanGate.KINDS[gate.kind], int(gate.per_channel), float(gate.tau),
          _ptr(gate.a_log), _ptr(gate.dt_bias), _ptr(skip), float(q_scale), cu_seqlens.data_ptr(), state_slots.data_ptr(),
-         num_seqs, heads, groups, key_dim, value_dim, stretches, _ptr(scratch), scratch.numel() if scratch is not None else 0,
-         _dtype_code(q), _stream())
+         num_seqs, t, heads, groups, key_dim, value_dim, stretches, _ptr(scratch),
+         scratch.numel() if scratch is not None else 0, _ptr(made), _dtype_code(q), _stream())
     return out
 
 
