@@ -5,7 +5,8 @@
 // from the request's state slot: `hist` float32 [taps - 1][width], oldest first, zero when the request starts
 // (which is "zeros before the start"). The slots lie `slot_stride` floats apart, so the history may be a slice of
 // a larger per-request state.
-//   short_conv        : out[t][c] = act(bias[c] + sum_j w[c][j] * in[t - (taps - 1 - j)][c]),  act: none or silu
+//   short_conv        : out[t][c] = act(bias[c] + sum_j w[j][c] * in[t - (taps - 1 - j)][c]),  act: none or silu
+//                       (the weights lie tap by tap, [taps][channels], so that neighbouring channels are neighbours)
 //   conv_qkv_append   : the same on the packed rows [q | k | v] of an attention layer, without bias or activation;
 //                       q is multiplied by its position's temperature 1 + coef * ln(floor((p + 1) / every) + 1)
 //                       and stored as [T][Hq][d]; k and v go to the token's row of its page: [k (d) | v (dv)], or,
@@ -27,7 +28,7 @@ __device__ __forceinline__ float conv_at(const T* __restrict__ in, int ld_in, in
         const int back = taps - 1 - j;
         const float v = local - back >= 0 ? to_f32(in[(size_t)(t - back) * ld_in + col])
                                           : hist[(size_t)(taps - 1 + local - back) * width + c];
-        acc = fmaf(w[(size_t)c * taps + j], v, acc);
+        acc = fmaf(w[(size_t)j * width + c], v, acc);
     }
     return acc;
 }
@@ -39,6 +40,136 @@ __device__ __forceinline__ void conv_shift_history(float* __restrict__ hist, int
     for (int j = 1; j < taps - 1; ++j) kept[j] = hist[(size_t)j * width + c];
     for (int j = 1; j < taps - 1; ++j) hist[(size_t)(j - 1) * width + c] = kept[j];
     hist[(size_t)(taps - 2) * width + c] = newest;
+}
+
+// ------------------------------------------------------------------ sixteen bytes of channels a thread
+// The *_vec kernels do the same as short_conv_kernel and conv_qkv_append_kernel for rows whose pieces (q, k, v, a
+// head) all start on 16-byte boundaries: a thread takes V = 16 / sizeof(T) neighbouring channels, one load per tap, one store.
+template <typename T, int V>
+__device__ __forceinline__ void load_row(const T* __restrict__ p, float* v) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < V; ++i) v[i] = to_f32(e[i]);
+}
+template <typename T, int V>
+__device__ __forceinline__ void store_row(T* __restrict__ p, const float* v) {
+    uint4 raw;
+    T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < V; ++i) e[i] = from_f32<T>(v[i]);
+    *reinterpret_cast<uint4*>(p) = raw;
+}
+
+// acc[i] = sum_j w[j][c0 + i] * in(t - (taps - 1 - j))[c0 + i]; newest[i]: the current token's own input.
+template <typename T, int V>
+__device__ __forceinline__ void conv_at_vec(const T* __restrict__ in, int ld_in, int col0, int t, int local,
+                                            const float* __restrict__ hist, int width, int c0,
+                                            const float* __restrict__ w, int taps, float* acc, float* newest) {
+#pragma unroll
+    for (int i = 0; i < V; ++i) acc[i] = 0.f;
+    for (int j = 0; j < taps; ++j) {
+        const int back = taps - 1 - j;
+        float v[V];
+        if (local - back >= 0) {
+            load_row<T, V>(in + (size_t)(t - back) * ld_in + col0, v);
+        } else {
+#pragma unroll
+            for (int i = 0; i < V; ++i) v[i] = hist[(size_t)(taps - 1 + local - back) * width + c0 + i];
+        }
+        float wj[V];
+        if (w) {
+#pragma unroll
+            for (int i = 0; i < V; i += 4) {
+                const float4 f = *reinterpret_cast<const float4*>(w + (size_t)j * width + c0 + i);
+                wj[i] = f.x; wj[i + 1] = f.y; wj[i + 2] = f.z; wj[i + 3] = f.w;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] = fmaf(w ? wj[i] : 1.f, v[i], acc[i]);
+        if (back == 0) {
+#pragma unroll
+            for (int i = 0; i < V; ++i) newest[i] = v[i];
+        }
+    }
+}
+
+template <typename T>
+__global__ void short_conv_vec_kernel(T* __restrict__ out, const T* __restrict__ in, int ld_in, int in_off,
+                                      const float* __restrict__ state, long long slot_stride, const float* __restrict__ w,
+                                      const float* __restrict__ bias, const int* __restrict__ token_seq,
+                                      const int* __restrict__ cu_seqlens, const int* __restrict__ state_slots, int width,
+                                      int taps, int act, int shift_history) {
+    constexpr int V = 16 / sizeof(T);
+    ti_grid_launch_dependents();
+    ti_grid_wait();
+    const int t = blockIdx.y;
+    const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * V;
+    if (c0 >= width) return;
+    const int seq = token_seq[t];
+    const int local = t - cu_seqlens[seq];
+    const float* hist = state + (size_t)state_slots[seq] * slot_stride;
+    float acc[V], newest[V];
+    conv_at_vec<T, V>(in, ld_in, in_off + c0, t, local, hist, width, c0, w, taps, acc, newest);
+    if (shift_history && taps > 1) {
+#pragma unroll
+        for (int i = 0; i < V; ++i) conv_shift_history(const_cast<float*>(hist), width, c0 + i, taps, newest[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+        if (bias) acc[i] += bias[c0 + i];
+        if (act == 1) acc[i] = acc[i] / (1.f + expf(-acc[i]));
+    }
+    store_row<T, V>(out + (size_t)t * width + c0, acc);
+}
+
+template <typename T>
+__global__ void conv_qkv_append_vec_kernel(T* __restrict__ q_out, T* __restrict__ cache, const T* __restrict__ qkv,
+                                           const float* __restrict__ state, long long slot_stride,
+                                           const float* __restrict__ w, int taps, float temp_coef, int temp_every,
+                                           const int* __restrict__ positions, const int* __restrict__ token_seq,
+                                           const int* __restrict__ cu_seqlens, const int* __restrict__ state_slots,
+                                           const int* __restrict__ block_table, int max_blocks, int hq, int hkv, int d,
+                                           int dv, int page_size, int num_pages, int row_stride, long long v_off,
+                                           int shift_history, int* __restrict__ status) {
+    constexpr int V = 16 / sizeof(T);
+    ti_grid_launch_dependents();
+    ti_grid_wait();
+    const int t = blockIdx.y;
+    const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * V;
+    const int cq = hq * d, ck = hkv * d, width = cq + ck + hkv * dv;
+    if (c0 >= width) return;
+    const int seq = token_seq[t];
+    const int local = t - cu_seqlens[seq];
+    const float* hist = taps > 1 ? state + (size_t)state_slots[seq] * slot_stride : nullptr;
+    float acc[V], newest[V];
+    conv_at_vec<T, V>(qkv, width, c0, t, local, hist, width, c0, w, taps, acc, newest);
+    if (shift_history && taps > 1) {
+#pragma unroll
+        for (int i = 0; i < V; ++i) conv_shift_history(const_cast<float*>(hist), width, c0 + i, taps, newest[i]);
+    }
+    const int pos = positions[t];
+    if (c0 < cq) {
+        if (temp_every > 0) {
+            const float f = 1.f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.f);
+#pragma unroll
+            for (int i = 0; i < V; ++i) acc[i] *= f;
+        }
+        store_row<T, V>(q_out + (size_t)t * cq + c0, acc);
+        return;
+    }
+    if (!cache) return;
+    const int logical = pos / page_size;
+    const int page = logical < max_blocks ? block_table[(size_t)seq * max_blocks + logical] : -1;
+    if (page < 0 || page >= num_pages) {
+        if (status) atomicExch(status, 1);                 // a token without a page
+        return;
+    }
+    int head;
+    long long off;
+    if (c0 < cq + ck) { head = (c0 - cq) / d; off = (c0 - cq) % d; }
+    else { head = (c0 - cq - ck) / dv; off = v_off + (c0 - cq - ck) % dv; }
+    store_row<T, V>(cache + (((size_t)page * hkv + head) * page_size + pos % page_size) * row_stride + off, acc);
 }
 
 template <typename T>
@@ -73,6 +204,21 @@ TI_API int ti_short_conv(void* out, const void* in, int ld_in, int in_off, float
     TI_REQUIRE(num_tokens <= 65535, "short_conv: more than 65535 tokens in one step");
     TI_REQUIRE(act == 0 || act == 1, "short_conv: unknown activation %d", act);
     if (num_tokens == 0) return 0;
+    // sixteen bytes of channels a thread where every piece allows it and the step has tokens enough to fill the machine so
+    const int vec = dtype == TI_F32 ? 4 : 8;
+    if (num_tokens >= 64 && width % vec == 0 && ld_in % vec == 0 && in_off % vec == 0 && ((uintptr_t)out | (uintptr_t)in | (uintptr_t)w) % 16 == 0) {
+        dim3 vgrid((width / vec + 127) / 128, num_tokens);
+        if (dtype == TI_F32)
+            ti_launch(short_conv_vec_kernel<float>, vgrid, 128, 0, stream, (float*)out, (const float*)in, ld_in, in_off,
+                      (const float*)state, slot_stride, w, bias, token_seq, cu_seqlens, state_slots, width, taps, act, shift_history);
+        else if (dtype == TI_BF16)
+            ti_launch(short_conv_vec_kernel<__nv_bfloat16>, vgrid, 128, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)in,
+                      ld_in, in_off, (const float*)state, slot_stride, w, bias, token_seq, cu_seqlens, state_slots, width, taps,
+                      act, shift_history);
+        else TI_REQUIRE(false, "short_conv: unknown dtype %d", dtype);
+        TI_CHECK_LAUNCH("short_conv");
+        return 0;
+    }
     dim3 grid((width + 127) / 128, num_tokens);
     if (dtype == TI_F32)
         ti_launch(short_conv_kernel<float>, grid, 128, 0, stream, (float*)out, (const float*)in, ld_in, in_off, (const float*)state, slot_stride,
@@ -143,7 +289,7 @@ __global__ void conv_qkv_append_kernel(T* __restrict__ q_out, T* __restrict__ ca
     const int local = t - cu_seqlens[seq];
     const float* hist = taps > 1 ? state + (size_t)state_slots[seq] * slot_stride : nullptr;
     float v = taps > 1 ? conv_at(qkv, width, c, t, local, hist, width, c, w, taps)
-                       : (w ? w[c] : 1.f) * to_f32(qkv[(size_t)t * width + c]);
+                       : (w ? w[c] : 1.f) * to_f32(qkv[(size_t)t * width + c]);     // one tap: [1][width]
     if (shift_history && taps > 1) conv_shift_history(const_cast<float*>(hist), width, c, taps, to_f32(qkv[(size_t)t * width + c]));
     const int pos = positions[t];
     if (c < cq) {
@@ -165,7 +311,7 @@ __global__ void conv_qkv_append_kernel(T* __restrict__ q_out, T* __restrict__ ca
     cache[(((size_t)page * hkv + head) * page_size + pos % page_size) * row_stride + off] = from_f32<T>(v);
 }
 
-// w: float32 [width][taps] over the packed channels (may be null with taps == 1: no convolution at all).
+// w: float32 [taps][width] over the packed channels (may be null with taps == 1: no convolution at all).
 // planes 1: cache [pages][hkv][page_size][d + dv]; planes 2 (d == dv): [2][pages][hkv][page_size][d].
 // shift_history: as in ti_short_conv.
 TI_API int ti_conv_qkv_append(void* q_out, void* cache, const void* qkv, float* state, long long slot_stride,
@@ -183,6 +329,23 @@ TI_API int ti_conv_qkv_append(void* q_out, void* cache, const void* qkv, float* 
     TI_REQUIRE(temp_every >= 0 && page_size > 0, "conv_qkv_append: bad constants");
     if (num_tokens == 0) return 0;
     const int width = hq * d + hkv * (d + dv);
+    const int vec = dtype == TI_F32 ? 4 : 8;
+    if (num_tokens >= 64 && d % vec == 0 && dv % vec == 0 && ((uintptr_t)q_out | (uintptr_t)cache | (uintptr_t)qkv | (uintptr_t)w) % 16 == 0) {
+        dim3 vgrid((width / vec + 127) / 128, num_tokens);
+        if (dtype == TI_F32)
+            ti_launch(conv_qkv_append_vec_kernel<float>, vgrid, 128, 0, stream, (float*)q_out, (float*)cache, (const float*)qkv,
+                      (const float*)state, slot_stride, w, taps, temp_coef, temp_every, positions, token_seq, cu_seqlens,
+                      state_slots, block_table, max_blocks, hq, hkv, d, dv, page_size, num_pages, row_stride, v_off,
+                      shift_history, status);
+        else if (dtype == TI_BF16)
+            ti_launch(conv_qkv_append_vec_kernel<__nv_bfloat16>, vgrid, 128, 0, stream, (__nv_bfloat16*)q_out,
+                      (__nv_bfloat16*)cache, (const __nv_bfloat16*)qkv, (const float*)state, slot_stride, w, taps, temp_coef,
+                      temp_every, positions, token_seq, cu_seqlens, state_slots, block_table, max_blocks, hq, hkv, d, dv,
+                      page_size, num_pages, row_stride, v_off, shift_history, status);
+        else TI_REQUIRE(false, "conv_qkv_append: unknown dtype %d", dtype);
+        TI_CHECK_LAUNCH("conv_qkv_append");
+        return 0;
+    }
     dim3 grid((width + 127) / 128, num_tokens);
     if (dtype == TI_F32)
         ti_launch(conv_qkv_append_kernel<float>, grid, 128, 0, stream, (float*)q_out, (float*)cache, (const float*)qkv, (const float*)state,

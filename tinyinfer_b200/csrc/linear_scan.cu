@@ -7,8 +7,8 @@
 //   gate 1 (sigmoid power) a = sigmoid(gate)^(1 / tau) = exp(logsigmoid(gate) / tau), per key channel
 //   gate 2 (step size)     dt = softplus(gate + dt_bias[h]), a = exp(-exp(A_log[h]) * dt) per head, and k_t is
 //                          multiplied by dt (a discretised state-space model: "Transformers are SSMs", Dao and Gu, 2024)
-// A small kernel makes the decays (and the keys' factors) of a step once, float32 [T][H * dk] or [T][H]; the scan reads
-// them like any other operand, so none of its blocks repeats a logarithm or an exponential.
+// For long portions a small kernel makes the decays (and the keys' factors) of the step once, float32 [T][H * dk] or
+// [T][H], and the scan reads them like any other operand; short steps make them while staging.
 // Decays, their logarithms, softplus, exponentials, the state and the outputs are float32; q, k and v are read in
 // the compute dtype from wherever they lie (row length and first column given), several heads may share one
 // group of q and k.
@@ -45,10 +45,14 @@ struct LinearScanArgs {
     const float* decay;       // float32 rows of ld_decay, first column decay_off: [H][dk] (per channel) or [H]
     int ld_decay, decay_off, per_channel;
     const float* kscale;      // float32 [T][H] or null: a factor on the keys of a head
+    int gate_mode;            // not LS_GATE_RAW: `decay` holds the gate's values and the decays are made while staging
+    float inv_tau;            // (short steps: a kernel of its own for them would cost more than repeating them a few times)
+    const float *a_log, *dt_bias;
     const float* skip;        // [H] or null
     float q_scale;
     const int *cu_seqlens, *state_slots;
     int heads, groups, dk, dv, kp, chunk;
+    int wide_state;           // the rows of a state start on 16-byte boundaries: a thread moves its rows four at a time
     int stretches;            // > 1: grid z is the stretch; part_b [request][stretch][H][dv][dk], part_a [request][stretch][H][dk]
     float *part_b, *part_a;
 };
@@ -93,11 +97,27 @@ __global__ void __launch_bounds__(LS_WARPS * 32) linear_scan_kernel(LinearScanAr
     float S[KPT], A[MODE == 1 ? KPT : 1];
 #pragma unroll
     for (int r = 0; r < KPT; ++r) {
-        const int idx = kpart * KPT + r;
-        S[r] = (MODE != 1 && col_ok && idx < a.dk) ? srow[idx] : 0.f;
+        S[r] = 0.f;
         if (MODE == 1) A[r] = 1.f;
     }
+    if (MODE != 1 && col_ok) {
+        if (a.wide_state) {
+#pragma unroll
+            for (int r = 0; r < KPT; r += 4) {
+                if (kpart * KPT + r < a.dk) {            // dk is a multiple of 4: the four are inside or outside together
+                    const float4 f = *reinterpret_cast<const float4*>(srow + kpart * KPT + r);
+                    S[r] = f.x; S[r + 1] = f.y; S[r + 2] = f.z; S[r + 3] = f.w;
+                }
+            }
+        } else {
+#pragma unroll
+            for (int r = 0; r < KPT; ++r)
+                if (kpart * KPT + r < a.dk) S[r] = srow[kpart * KPT + r];
+        }
+    }
     const float skip = a.skip ? a.skip[h] : 0.f;
+    const float rate = a.gate_mode == LS_GATE_STEP ? expf(a.a_log[h]) : 0.f;
+    const float dt_bias = a.gate_mode == LS_GATE_STEP && a.dt_bias ? a.dt_bias[h] : 0.f;
 
     for (int t0 = row0; t0 < row1; t0 += a.chunk) {
         const int n = min(a.chunk, row1 - t0);
@@ -110,6 +130,13 @@ __global__ void __launch_bounds__(LS_WARPS * 32) linear_scan_kernel(LinearScanAr
                 kv = to_f32(k[(size_t)t * a.ld_k + a.k_off + g * a.dk + idx]);
                 if (a.kscale) kv *= a.kscale[(size_t)t * a.heads + h];
                 av = a.decay[(size_t)t * a.ld_decay + a.decay_off + (a.per_channel ? h * a.dk + idx : h)];
+                if (a.gate_mode == LS_GATE_SIGMOID_POW) {
+                    av = expf(ls_logsigmoid(av) * a.inv_tau);
+                } else if (a.gate_mode == LS_GATE_STEP) {
+                    const float dt = ls_softplus(av + dt_bias);
+                    av = expf(-rate * dt);
+                    kv *= dt;
+                }
             }
             const int at = tt * trow + (idx / KPT) * PITCH + idx % KPT;
             sq[at] = qv;
@@ -154,10 +181,15 @@ __global__ void __launch_bounds__(LS_WARPS * 32) linear_scan_kernel(LinearScanAr
     }
     if (MODE == 2) return;
     if (col_ok) {
+        if (a.wide_state) {
 #pragma unroll
-        for (int r = 0; r < KPT; ++r) {
-            const int idx = kpart * KPT + r;
-            if (idx < a.dk) srow[idx] = S[r];
+            for (int r = 0; r < KPT; r += 4)
+                if (kpart * KPT + r < a.dk)
+                    *reinterpret_cast<float4*>(srow + kpart * KPT + r) = make_float4(S[r], S[r + 1], S[r + 2], S[r + 3]);
+        } else {
+#pragma unroll
+            for (int r = 0; r < KPT; ++r)
+                if (kpart * KPT + r < a.dk) srow[kpart * KPT + r] = S[r];
         }
     }
     if (MODE == 1 && cb == 0 && warp == 0 && lane < KP) {           // the stretch's product of decays, once a head
@@ -246,12 +278,13 @@ TI_API int ti_linear_scan(float* y, float* state, long long slot_stride, const v
     TI_REQUIRE(stretches == 1 || (scratch && scratch_floats >= ti_linear_scan_scratch_floats(num_seqs, heads, dk, dv, stretches)),
                "linear_scan: %d stretches need %lld floats of scratch", stretches,
                ti_linear_scan_scratch_floats(num_seqs, heads, dk, dv, stretches));
-    TI_REQUIRE(gate_mode == LS_GATE_RAW || gate_out, "linear_scan: the decays need a place to be made in");
+    TI_REQUIRE(gate_mode == LS_GATE_RAW || stretches == 1 || gate_out, "linear_scan: the decays need a place to be made in");
     if (num_seqs == 0 || num_tokens == 0) return 0;
     const float* decay = gate;
     const float* kscale = nullptr;
     int ld_decay = ld_gate, decay_off = gate_off;
-    if (gate_mode != LS_GATE_RAW) {
+    const bool gate_apart = gate_mode != LS_GATE_RAW && stretches > 1;      // long portions: the decays are made once
+    if (gate_apart) {
         const int per_head = gate_per_channel ? dk : 1;
         const size_t n = (size_t)num_tokens * heads * per_head;
         ti_launch(scan_gate_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, gate_out, gate_out + n, gate, ld_gate, gate_off,
@@ -272,8 +305,10 @@ TI_API int ti_linear_scan(float* y, float* state, long long slot_stride, const v
     while (chunk > 1 && (size_t)chunk * (3 * trow + cols_per_block) * sizeof(float) > 40 * 1024) chunk >>= 1;
     const size_t smem = (size_t)chunk * (3 * trow + cols_per_block) * sizeof(float);
     LinearScanArgs a = {y, state, slot_stride, q, k, v, ld_q, q_off, ld_k, k_off, ld_v, v_off, decay, ld_decay, decay_off,
-                        gate_per_channel, kscale, skip, q_scale, cu_seqlens, state_slots,
-                        heads, groups, dk, dv, kp, chunk, stretches, scratch,
+                        gate_per_channel, kscale, gate_apart ? LS_GATE_RAW : gate_mode,
+                        gate_mode == LS_GATE_SIGMOID_POW ? 1.f / tau : 0.f, a_log, dt_bias, skip, q_scale, cu_seqlens, state_slots,
+                        heads, groups, dk, dv, kp, chunk,
+                        dk % 4 == 0 && slot_stride % 4 == 0 && ((uintptr_t)state | (uintptr_t)scratch) % 16 == 0, stretches, scratch,
                         scratch ? scratch + (long long)num_seqs * stretches * heads * dk * dv : nullptr};
     dim3 grid(heads * ((dv + cols_per_block - 1) / cols_per_block), num_seqs, stretches);
     typedef __nv_bfloat16 B;

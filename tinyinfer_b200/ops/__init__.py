@@ -1156,13 +1156,13 @@ def short_conv(x: torch.Tensor, *, offset: int, width: int, history: torch.Tenso
                bias: Optional[torch.Tensor], silu: bool, token_seq: torch.Tensor, cu_seqlens: torch.Tensor,
                state_slots: torch.Tensor, shift_history: bool = False) -> torch.Tensor:
     """Causal per-channel convolution over time of columns [offset, offset + width) of ``x`` [T, row], ``weight``
-    float32 [width, taps] (last column: the current token), then + bias and silu if asked. Inputs of earlier steps
+    float32 [taps, width] (tap by tap; the last row meets the current token), then + bias and silu if asked. Inputs of earlier steps
     come from ``history`` float32 [slots, taps - 1, width] (oldest first), which ``conv_state_update`` keeps; in a
     step in which EVERY request brings one token, ``shift_history`` lets this kernel move the histories on itself."""
     _check(x, "x", None, 2)
     _check(weight, "weight", torch.float32, 2)
-    taps = weight.shape[1]
-    if weight.shape[0] != width or offset + width > x.shape[1]:
+    taps = weight.shape[0]
+    if weight.shape[1] != width or offset + width > x.shape[1]:
         raise KernelError("short_conv: shapes do not match")
     stride = _slot_stride(history, (taps - 1) * width, "history") if taps > 1 else 0
     if bias is not None:
@@ -1204,7 +1204,7 @@ def conv_qkv_append(qkv: torch.Tensor, *, num_heads: int, num_kv_heads: int, hea
                     block_table: torch.Tensor, status: Optional[torch.Tensor] = None,
                     shift_history: bool = False) -> torch.Tensor:
     """``qkv`` [T, Hq d + Hkv (d + dv)] packed [q | k | v]: a short causal convolution per channel
-    (``conv_weight`` float32 [channels, taps] with ``history`` float32 [slots, taps - 1, channels]; None: none),
+    (``conv_weight`` float32 [taps, channels], tap by tap, with ``history`` float32 [slots, taps - 1, channels]; None: none),
     then q times its position's temperature 1 + coef * ln(floor((p + 1) / every) + 1) (``temperature`` =
     (coef, every) or None). Returns q [T, Hq, d]; k and v go to the token's row [k | v] of ``cache``
     [1, pages, Hkv, page, d + dv], or, where d == dv, to the planes of a cache [2, pages, Hkv, page, d].
@@ -1217,9 +1217,9 @@ def conv_qkv_append(qkv: torch.Tensor, *, num_heads: int, num_kv_heads: int, hea
     taps, stride = 1, 0
     if conv_weight is not None:
         _check(conv_weight, "conv_weight", torch.float32, 2)
-        taps = conv_weight.shape[1]
-        if conv_weight.shape[0] != width:
-            raise KernelError("conv_qkv_append: one row of taps per packed channel")
+        taps = conv_weight.shape[0]
+        if conv_weight.shape[1] != width:
+            raise KernelError("conv_qkv_append: every tap has a weight per packed channel")
         if taps > 1:
             stride = _slot_stride(history, (taps - 1) * width, "history")
     _check(positions, "positions", torch.int32, 1)
@@ -1330,7 +1330,7 @@ def linear_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: ScanGat
         fn.restype = ctypes.c_longlong
         scratch = torch.empty(int(fn(num_seqs, heads, key_dim, value_dim, stretches)), dtype=torch.float32, device=q.device)
     made = None          # the decays (and the keys' factors) as the scan reads them, unless the gate holds them already
-    if gate.kind != "raw":
+    if gate.kind != "raw" and stretches > 1:
         made = torch.empty(t * heads * (key_dim if gate.per_channel else 1) * (2 if gate.kind == "step_size" else 1),
                            dtype=torch.float32, device=q.device)
     _run("hybrid", "ti_linear_scan", out.data_ptr(), state.data_ptr(), stride, q.data_ptr(), q.shape[1], q_offset,

@@ -65,7 +65,8 @@ class ConvAttention(Mixer):
             self.b_qkv = torch.cat([tensors["q.b"], tensors["k.b"], tensors["v.b"]]).contiguous()
             self.b_o = tensors["o.b"]
         if s.conv_taps >= 1:
-            self.conv_w = torch.cat([tensors["q.conv"], tensors["k.conv"], tensors["v.conv"]], dim=0).contiguous()
+            # tap by tap, [taps, channels]: neighbouring channels are neighbours in memory, as the kernel reads them
+            self.conv_w = torch.cat([tensors["q.conv"], tensors["k.conv"], tensors["v.conv"]], dim=0).t().contiguous()
 
     def _attend(self, x, step, cache, out_scale=1.0):
         s = self.spec

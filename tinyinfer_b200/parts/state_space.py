@@ -52,7 +52,7 @@ class StateSpace(Mixer):
         cut = s.inner_size + s.conv_size
         self.w_main = tensors["in"][:cut].contiguous()          # [z | x | B | C]
         self.w_dt = tensors["in"][cut:].contiguous()            # the step sizes: their product stays float32
-        self.conv_w, self.conv_b = tensors["conv"].contiguous(), tensors["conv.b"]
+        self.conv_w, self.conv_b = tensors["conv"].t().contiguous(), tensors["conv.b"]      # tap by tap, [taps, channels]
         self.dt_bias, self.a_log, self.skip = tensors["dt_bias"], tensors["A_log"], tensors["D"]
         self.norm_w, self.w_o = tensors["norm"], tensors["o"].contiguous()
 
