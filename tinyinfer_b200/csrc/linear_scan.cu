@@ -379,12 +379,75 @@ __global__ void gated_group_norm_kernel(T* __restrict__ out, const float* __rest
     }
 }
 
+// The same with a warp per (token, group) and four neighbouring features a lane a trip (groups of a multiple of four
+// features, rows on 16-byte boundaries): no block-wide barrier, 16-byte loads of y.
+template <typename T>
+__global__ void gated_group_norm_warp_kernel(T* __restrict__ out, const float* __restrict__ y, const T* __restrict__ gate,
+                                             int ld_gate, int gate_off, const float* __restrict__ w, int w_len, int width,
+                                             int group, float eps, int gate_first, float out_scale, long long num_groups) {
+    ti_grid_launch_dependents();
+    ti_grid_wait();
+    const long long gi = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (gi >= num_groups) return;
+    const int lane = threadIdx.x & 31, per_row = width / group;
+    const long long t = gi / per_row;
+    const int g0 = (int)(gi % per_row) * group;
+    const float* yrow = y + (size_t)t * width + g0;
+    const T* grow = gate ? gate + (size_t)t * ld_gate + gate_off + g0 : nullptr;
+    auto gates = [&](int i, float* gz) {
+        if (!grow) { gz[0] = gz[1] = gz[2] = gz[3] = 1.f; return; }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float z = to_f32(grow[i + e]);
+            gz[e] = z / (1.f + expf(-z));
+        }
+    };
+    float ss = 0.f;
+    for (int i = lane * 4; i < group; i += 128) {
+        const float4 f = *reinterpret_cast<const float4*>(yrow + i);
+        float v[4] = {f.x, f.y, f.z, f.w};
+        if (gate_first) {
+            float gz[4];
+            gates(i, gz);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[e] *= gz[e];
+        }
+        ss += v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+    }
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)group + eps) * out_scale;
+    for (int i = lane * 4; i < group; i += 128) {
+        const float4 f = *reinterpret_cast<const float4*>(yrow + i);
+        float v[4] = {f.x, f.y, f.z, f.w}, gz[4];
+        gates(i, gz);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            float x = gate_first ? v[e] * gz[e] : v[e];
+            x = x * inv * w[(g0 + i + e) % w_len];
+            out[(size_t)t * width + g0 + i + e] = from_f32<T>(gate_first ? x : x * gz[e]);
+        }
+    }
+}
+
 TI_API int ti_gated_group_norm(void* out, const float* y, const void* gate, int ld_gate, int gate_off, const float* w,
                                int w_len, int num_tokens, int width, int group, float eps, int gate_first, float out_scale,
                                int dtype, cudaStream_t stream) {
     TI_REQUIRE(num_tokens >= 0 && width > 0 && group > 0 && width % group == 0 && w_len > 0, "gated_group_norm: bad sizes");
     TI_REQUIRE(width / group <= 65535, "gated_group_norm: too many groups");
     if (num_tokens == 0) return 0;
+    if (group % 4 == 0 && group <= 8192 && (uintptr_t)y % 16 == 0) {          // a warp a group
+        const long long num_groups = (long long)num_tokens * (width / group);
+        const unsigned blocks = (unsigned)((num_groups + 7) / 8);
+        if (dtype == TI_F32)
+            ti_launch(gated_group_norm_warp_kernel<float>, blocks, 256, 0, stream, (float*)out, y, (const float*)gate, ld_gate,
+                      gate_off, w, w_len, width, group, eps, gate_first, out_scale, num_groups);
+        else if (dtype == TI_BF16)
+            ti_launch(gated_group_norm_warp_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)out, y,
+                      (const __nv_bfloat16*)gate, ld_gate, gate_off, w, w_len, width, group, eps, gate_first, out_scale, num_groups);
+        else TI_REQUIRE(false, "gated_group_norm: unknown dtype %d", dtype);
+        TI_CHECK_LAUNCH("gated_group_norm");
+        return 0;
+    }
     int threads = 32;
     while (threads < 256 && threads < group) threads <<= 1;
     dim3 grid(num_tokens, width / group);
