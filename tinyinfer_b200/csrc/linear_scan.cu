@@ -435,7 +435,7 @@ TI_API int ti_gated_group_norm(void* out, const float* y, const void* gate, int 
     TI_REQUIRE(num_tokens >= 0 && width > 0 && group > 0 && width % group == 0 && w_len > 0, "gated_group_norm: bad sizes");
     TI_REQUIRE(width / group <= 65535, "gated_group_norm: too many groups");
     if (num_tokens == 0) return 0;
-    if (group % 4 == 0 && group <= 8192 && (uintptr_t)y % 16 == 0) {          // a warp a group
+    if (group % 4 == 0 && group <= 512 && (uintptr_t)y % 16 == 0) {          // a warp a group; larger groups: a block
         const long long num_groups = (long long)num_tokens * (width / group);
         const unsigned blocks = (unsigned)((num_groups + 7) / 8);
         if (dtype == TI_F32)
