@@ -21,10 +21,12 @@
 // memory by the whole block.
 //
 // Long portions are cut into stretches that run side by side (grid z), since the recurrence composes: a stretch is
-// (A, B) = (the product of its decays, its own scan from a zero state). Pass 1 scans every stretch from zero and
-// leaves (A, B); a fold walks a request's stretches in order, S <- A S + B, leaves each stretch's true starting state
-// where its B was and the request's new state in its slot; pass 2 scans every stretch again from its true start and
-// writes the outputs. Twice the arithmetic, as many times the blocks as there are stretches.
+// (A, B) = (the product of its decays, its own scan from a zero state). Pass 1 scans every stretch from zero, writes
+// the outputs that its own tokens give, leaves (A, B) and, per token, q times the product of the decays so far; a fold
+// walks a request's stretches in order, S <- A S + B, leaves each stretch's true starting state where its B was and
+// the request's new state in its slot; pass 2 adds to every output what the state at the stretch's start gives it,
+// o_t += (q_t * D_t)^T S_start with D_t the product of the stretch's decays up to t: a plain product, no recurrence.
+// Four thirds of the arithmetic, as many times the blocks as there are stretches.
 //
 //   gated_group_norm : out = scale * w * n(y) * silu(gate)  or  scale * w * n(y * silu(gate)),  n: every group of
 //                      `group` features divided by its root mean square (float32), one rounding
@@ -55,12 +57,13 @@ struct LinearScanArgs {
     int wide_state;           // the rows of a state start on 16-byte boundaries: a thread moves its rows four at a time
     int stretches;            // > 1: grid z is the stretch; part_b [request][stretch][H][dv][dk], part_a [request][stretch][H][dk]
     float *part_b, *part_a;
+    float* qd;                // [T][H][dk]: q times the product of the decays from the stretch's start to the token
 };
 
-// MODE 0: from the slot's state to the slot's state, with outputs; 1: a stretch from zero, leaves (A, B), no outputs;
-// 2: a stretch from the start the fold left, with outputs.
+// MODE 0: from the slot's state to the slot's state, with outputs; 1: a stretch from zero, with the outputs its own
+// tokens give, leaves (A, B) and qd; 2: adds what the state at the stretch's start gives every output.
 template <typename T, int KPT, int MODE>
-__global__ void __launch_bounds__(LS_WARPS * 32) linear_scan_kernel(LinearScanArgs a) {
+__global__ void __launch_bounds__(LS_WARPS * 32, KPT <= 16 ? 7 : 1) linear_scan_kernel(LinearScanArgs a) {      // seven blocks an SM: what the stretches are counted for
     extern __shared__ float smem[];
     ti_grid_launch_dependents();
     ti_grid_wait();
@@ -94,12 +97,17 @@ __global__ void __launch_bounds__(LS_WARPS * 32) linear_scan_kernel(LinearScanAr
     const size_t in_head = ((size_t)h * a.dv + (col_ok ? col : 0)) * a.dk;
     float* srow = MODE == 0 ? a.state + (size_t)a.state_slots[seq] * a.slot_stride + in_head
                             : a.part_b + ((size_t)seq * a.stretches + blockIdx.z) * a.heads * a.dv * a.dk + in_head;
-    float S[KPT], A[MODE == 1 ? KPT : 1];
+    float S[KPT];
+    // Mode 1, the block of a head's first columns: thread i (and i + 128, ...) carries the product D of key channel i's
+    // decays from the stretch's start, chunk by chunk, and writes q * D for every token; at the end D is the stretch's A.
+    constexpr int DPT = 8;                               // 1,024 key channels over 128 threads
+    float D[MODE == 1 ? DPT : 1];
+    if (MODE == 1) {
 #pragma unroll
-    for (int r = 0; r < KPT; ++r) {
-        S[r] = 0.f;
-        if (MODE == 1) A[r] = 1.f;
+        for (int i = 0; i < DPT; ++i) D[i] = 1.f;
     }
+#pragma unroll
+    for (int r = 0; r < KPT; ++r) S[r] = 0.f;
     if (MODE != 1 && col_ok) {
         if (a.wide_state) {
 #pragma unroll
@@ -122,60 +130,119 @@ __global__ void __launch_bounds__(LS_WARPS * 32) linear_scan_kernel(LinearScanAr
     for (int t0 = row0; t0 < row1; t0 += a.chunk) {
         const int n = min(a.chunk, row1 - t0);
         __syncthreads();                                 // the chunk before has been read
-        for (int e = tid; e < n * dkp; e += LS_WARPS * 32) {
-            const int tt = e / dkp, idx = e % dkp, t = t0 + tt;
-            float qv = 0.f, kv = 0.f, av = 1.f;
-            if (idx < a.dk) {
-                qv = to_f32(q[(size_t)t * a.ld_q + a.q_off + g * a.dk + idx]) * a.q_scale;
-                kv = to_f32(k[(size_t)t * a.ld_k + a.k_off + g * a.dk + idx]);
-                if (a.kscale) kv *= a.kscale[(size_t)t * a.heads + h];
-                av = a.decay[(size_t)t * a.ld_decay + a.decay_off + (a.per_channel ? h * a.dk + idx : h)];
-                if (a.gate_mode == LS_GATE_SIGMOID_POW) {
-                    av = expf(ls_logsigmoid(av) * a.inv_tau);
-                } else if (a.gate_mode == LS_GATE_STEP) {
-                    const float dt = ls_softplus(av + dt_bias);
-                    av = expf(-rate * dt);
-                    kv *= dt;
+        // Several elements a thread a trip, all their loads issued before the first is used: a trip that waits for its
+        // three loads before it starts the next one is what a chunk's time went into. (Eight a trip where only qd is
+        // read; four elsewhere: the registers they take are blocks an SM.)
+        constexpr int U = MODE == 2 ? 8 : 4;
+        for (int e0 = tid; e0 < n * dkp; e0 += LS_WARPS * 32 * U) {
+            float qv[U], kv[U], av[U], ks[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int e = e0 + u * LS_WARPS * 32;
+                const int tt = e / dkp, idx = e % dkp, t = t0 + tt;
+                qv[u] = 0.f; kv[u] = 0.f; av[u] = 1.f; ks[u] = 1.f;
+                if (e < n * dkp && idx < a.dk) {
+                    if (MODE == 2) {
+                        qv[u] = a.qd[((size_t)t * a.heads + h) * a.dk + idx];
+                    } else {
+                        qv[u] = to_f32(q[(size_t)t * a.ld_q + a.q_off + g * a.dk + idx]);
+                        kv[u] = to_f32(k[(size_t)t * a.ld_k + a.k_off + g * a.dk + idx]);
+                        if (a.kscale) ks[u] = a.kscale[(size_t)t * a.heads + h];
+                        av[u] = a.decay[(size_t)t * a.ld_decay + a.decay_off + (a.per_channel ? h * a.dk + idx : h)];
+                    }
                 }
             }
-            const int at = tt * trow + (idx / KPT) * PITCH + idx % KPT;
-            sq[at] = qv;
-            sk[at] = kv;
-            sa[at] = av;
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int e = e0 + u * LS_WARPS * 32;
+                if (e >= n * dkp) continue;
+                const int tt = e / dkp, idx = e % dkp;
+                float qs = qv[u], kk = kv[u] * ks[u], aa = av[u];
+                if (MODE != 2 && idx < a.dk) {
+                    qs *= a.q_scale;
+                    if (a.gate_mode == LS_GATE_SIGMOID_POW) {
+                        aa = expf(ls_logsigmoid(aa) * a.inv_tau);
+                    } else if (a.gate_mode == LS_GATE_STEP) {
+                        const float dt = ls_softplus(aa + dt_bias);
+                        aa = expf(-rate * dt);
+                        kk *= dt;
+                    }
+                }
+                const int at = tt * trow + (idx / KPT) * PITCH + idx % KPT;
+                sq[at] = qs;
+                if (MODE != 2) {
+                    sk[at] = kk;
+                    sa[at] = aa;
+                }
+            }
         }
-        for (int e = tid; e < n * cols_per_block; e += LS_WARPS * 32) {
-            const int tt = e / cols_per_block, c = cb * cols_per_block + e % cols_per_block;
-            sv[e] = c < a.dv ? to_f32(v[(size_t)(t0 + tt) * a.ld_v + a.v_off + h * a.dv + c]) : 0.f;
+        // the values' columns of this block; in mode 2 the outputs so far, which the state's share is added to
+        for (int e0 = tid; e0 < n * cols_per_block; e0 += LS_WARPS * 32 * 4) {
+            float got[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int e = e0 + u * LS_WARPS * 32;
+                const int tt = e / cols_per_block, c = cb * cols_per_block + e % cols_per_block;
+                got[u] = 0.f;
+                if (e < n * cols_per_block && c < a.dv)
+                    got[u] = MODE == 2 ? a.y[(size_t)(t0 + tt) * a.heads * a.dv + h * a.dv + c]
+                                       : to_f32(v[(size_t)(t0 + tt) * a.ld_v + a.v_off + h * a.dv + c]);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int e = e0 + u * LS_WARPS * 32;
+                if (e < n * cols_per_block) sv[e] = got[u];
+            }
         }
         __syncthreads();
+        if (MODE == 1 && cb == 0) {
+#pragma unroll
+            for (int i = 0; i < DPT; ++i) {
+                const int idx = tid + i * LS_WARPS * 32;
+                if (idx < a.dk) {
+                    const int at0 = (idx / KPT) * PITCH + idx % KPT;
+                    float d = D[MODE == 1 ? i : 0];
+                    for (int tt = 0; tt < n; ++tt) {
+                        d *= sa[tt * trow + at0];
+                        a.qd[((size_t)(t0 + tt) * a.heads + h) * a.dk + idx] = sq[tt * trow + at0] * d;
+                    }
+                    D[MODE == 1 ? i : 0] = d;
+                }
+            }
+        }
         for (int tt = 0; tt < n; ++tt) {
-            const float vv = sv[tt * cols_per_block + warp * cols_per_warp + lane / KP];
+            const float vv = sv[tt * cols_per_block + warp * cols_per_warp + lane / KP];     // mode 2: the output so far
             const float4* pq = reinterpret_cast<const float4*>(sq + (size_t)tt * trow + kpart * PITCH);
             const float4* pk = reinterpret_cast<const float4*>(sk + (size_t)tt * trow + kpart * PITCH);
             const float4* pa = reinterpret_cast<const float4*>(sa + (size_t)tt * trow + kpart * PITCH);
             float o = 0.f, o2 = 0.f;
 #pragma unroll
             for (int r4 = 0; r4 < KPT / 4; ++r4) {
+                const float4 qv = pq[r4];
+                const float qr[4] = {qv.x, qv.y, qv.z, qv.w};
+                if (MODE == 2) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (j & 1) o2 = fmaf(S[r4 * 4 + j], qr[j], o2);
+                        else o = fmaf(S[r4 * 4 + j], qr[j], o);
+                    }
+                    continue;
+                }
                 const float4 av = pa[r4], kv = pk[r4];
                 const float ar[4] = {av.x, av.y, av.z, av.w}, kr[4] = {kv.x, kv.y, kv.z, kv.w};
-                float qr[4] = {0.f, 0.f, 0.f, 0.f};
-                if (MODE != 1) {
-                    const float4 qv = pq[r4];
-                    qr[0] = qv.x; qr[1] = qv.y; qr[2] = qv.z; qr[3] = qv.w;
-                }
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int r = r4 * 4 + j;
                     S[r] = fmaf(ar[j], S[r], kr[j] * vv);
-                    if (MODE == 1) A[r] *= ar[j];
-                    else if (j & 1) o2 = fmaf(S[r], qr[j], o2);
+                    if (j & 1) o2 = fmaf(S[r], qr[j], o2);
                     else o = fmaf(S[r], qr[j], o);
                 }
             }
-            if (MODE != 1) {
-                o += o2;
-                for (int off = 1; off < KP; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
-                if (kpart == 0 && col_ok) a.y[(size_t)(t0 + tt) * a.heads * a.dv + h * a.dv + col] = fmaf(skip, vv, o);
+            o += o2;
+            for (int off = 1; off < KP; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+            if (kpart == 0 && col_ok) {
+                float* dst = a.y + (size_t)(t0 + tt) * a.heads * a.dv + h * a.dv + col;
+                *dst = MODE == 2 ? vv + o : fmaf(skip, vv, o);
             }
         }
     }
@@ -192,12 +259,12 @@ __global__ void __launch_bounds__(LS_WARPS * 32) linear_scan_kernel(LinearScanAr
                 if (kpart * KPT + r < a.dk) srow[kpart * KPT + r] = S[r];
         }
     }
-    if (MODE == 1 && cb == 0 && warp == 0 && lane < KP) {           // the stretch's product of decays, once a head
+    if (MODE == 1 && cb == 0) {                          // the stretch's product of decays, once a head
         float* arow = a.part_a + (((size_t)seq * a.stretches + blockIdx.z) * a.heads + h) * a.dk;
 #pragma unroll
-        for (int r = 0; r < KPT; ++r) {
-            const int idx = kpart * KPT + r;
-            if (idx < a.dk) arow[idx] = A[r];
+        for (int i = 0; i < DPT; ++i) {
+            const int idx = tid + i * LS_WARPS * 32;
+            if (idx < a.dk) arow[idx] = D[MODE == 1 ? i : 0];
         }
     }
 }
@@ -254,8 +321,8 @@ __global__ void scan_gate_kernel(float* __restrict__ decay, float* __restrict__ 
     }
 }
 
-TI_API long long ti_linear_scan_scratch_floats(int num_seqs, int heads, int dk, int dv, int stretches) {
-    return stretches > 1 ? (long long)num_seqs * stretches * heads * dk * (dv + 1) : 0;
+TI_API long long ti_linear_scan_scratch_floats(int num_seqs, int num_tokens, int heads, int dk, int dv, int stretches) {
+    return stretches > 1 ? (long long)num_seqs * stretches * heads * dk * (dv + 1) + (long long)num_tokens * heads * dk : 0;
 }
 
 // gate_mode 0: `gate` holds the decays themselves. Otherwise they are made first, into `gate_out` (float32, as many
@@ -275,9 +342,9 @@ TI_API int ti_linear_scan(float* y, float* state, long long slot_stride, const v
     TI_REQUIRE(gate_mode != LS_GATE_SIGMOID_POW || tau > 0.f, "linear_scan: tau must be positive");
     TI_REQUIRE(num_seqs <= 65535, "linear_scan: too many requests");
     TI_REQUIRE(stretches >= 1 && stretches <= 1024, "linear_scan: %d stretches", stretches);
-    TI_REQUIRE(stretches == 1 || (scratch && scratch_floats >= ti_linear_scan_scratch_floats(num_seqs, heads, dk, dv, stretches)),
+    TI_REQUIRE(stretches == 1 || (scratch && scratch_floats >= ti_linear_scan_scratch_floats(num_seqs, num_tokens, heads, dk, dv, stretches)),
                "linear_scan: %d stretches need %lld floats of scratch", stretches,
-               ti_linear_scan_scratch_floats(num_seqs, heads, dk, dv, stretches));
+               ti_linear_scan_scratch_floats(num_seqs, num_tokens, heads, dk, dv, stretches));
     TI_REQUIRE(gate_mode == LS_GATE_RAW || stretches == 1 || gate_out, "linear_scan: the decays need a place to be made in");
     if (num_seqs == 0 || num_tokens == 0) return 0;
     const float* decay = gate;
@@ -309,7 +376,8 @@ TI_API int ti_linear_scan(float* y, float* state, long long slot_stride, const v
                         gate_mode == LS_GATE_SIGMOID_POW ? 1.f / tau : 0.f, a_log, dt_bias, skip, q_scale, cu_seqlens, state_slots,
                         heads, groups, dk, dv, kp, chunk,
                         dk % 4 == 0 && slot_stride % 4 == 0 && ((uintptr_t)state | (uintptr_t)scratch) % 16 == 0, stretches, scratch,
-                        scratch ? scratch + (long long)num_seqs * stretches * heads * dk * dv : nullptr};
+                        scratch ? scratch + (long long)num_seqs * stretches * heads * dk * dv : nullptr,
+                        scratch ? scratch + (long long)num_seqs * stretches * heads * dk * (dv + 1) : nullptr};
     dim3 grid(heads * ((dv + cols_per_block - 1) / cols_per_block), num_seqs, stretches);
     typedef __nv_bfloat16 B;
 #define TI_SCAN(KPT, MODE)                                                                                          \
@@ -337,7 +405,7 @@ TI_API int ti_linear_scan(float* y, float* state, long long slot_stride, const v
               (const float*)a.part_a, state_slots, stretches, heads, dk, dv);
     TI_CHECK_LAUNCH("linear_scan (fold)");
     TI_SCAN_PASS(2);
-    TI_CHECK_LAUNCH("linear_scan (stretches from their starts)");
+    TI_CHECK_LAUNCH("linear_scan (what the stretches' starts give)");
 #undef TI_SCAN_PASS
 #undef TI_SCAN
     return 0;
@@ -380,11 +448,14 @@ __global__ void gated_group_norm_kernel(T* __restrict__ out, const float* __rest
 }
 
 // The same with a warp per (token, group) and four neighbouring features a lane a trip (groups of a multiple of four
-// features, rows on 16-byte boundaries): no block-wide barrier, 16-byte loads of y.
+// features up to 512, rows on 16-byte boundaries): y and the gate are read once and kept in registers, no block-wide
+// barrier, 16-byte loads of y, one store per four features.
 template <typename T>
 __global__ void gated_group_norm_warp_kernel(T* __restrict__ out, const float* __restrict__ y, const T* __restrict__ gate,
                                              int ld_gate, int gate_off, const float* __restrict__ w, int w_len, int width,
-                                             int group, float eps, int gate_first, float out_scale, long long num_groups) {
+                                             int group, float eps, int gate_first, float out_scale, long long num_groups,
+                                             int wide_rows) {
+    constexpr int TRIPS = 4;                             // 4 trips x 32 lanes x 4 features = 512
     ti_grid_launch_dependents();
     ti_grid_wait();
     const long long gi = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -394,37 +465,49 @@ __global__ void gated_group_norm_warp_kernel(T* __restrict__ out, const float* _
     const int g0 = (int)(gi % per_row) * group;
     const float* yrow = y + (size_t)t * width + g0;
     const T* grow = gate ? gate + (size_t)t * ld_gate + gate_off + g0 : nullptr;
-    auto gates = [&](int i, float* gz) {
-        if (!grow) { gz[0] = gz[1] = gz[2] = gz[3] = 1.f; return; }
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const float z = to_f32(grow[i + e]);
-            gz[e] = z / (1.f + expf(-z));
-        }
-    };
+    float v[TRIPS][4], gz[TRIPS][4];
     float ss = 0.f;
-    for (int i = lane * 4; i < group; i += 128) {
-        const float4 f = *reinterpret_cast<const float4*>(yrow + i);
-        float v[4] = {f.x, f.y, f.z, f.w};
-        if (gate_first) {
-            float gz[4];
-            gates(i, gz);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) v[e] *= gz[e];
+    for (int k = 0; k < TRIPS; ++k) {
+        const int i = k * 128 + lane * 4;
+        if (i < group) {
+            const float4 f = *reinterpret_cast<const float4*>(yrow + i);
+            v[k][0] = f.x; v[k][1] = f.y; v[k][2] = f.z; v[k][3] = f.w;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float z = grow ? to_f32(grow[i + e]) : 0.f;
+                gz[k][e] = grow ? z / (1.f + expf(-z)) : 1.f;
+                if (gate_first) v[k][e] *= gz[k][e];
+                ss += v[k][e] * v[k][e];
+            }
         }
-        ss += v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
     }
     ss = warp_sum(ss);
     const float inv = rsqrtf(ss / (float)group + eps) * out_scale;
-    for (int i = lane * 4; i < group; i += 128) {
-        const float4 f = *reinterpret_cast<const float4*>(yrow + i);
-        float v[4] = {f.x, f.y, f.z, f.w}, gz[4];
-        gates(i, gz);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            float x = gate_first ? v[e] * gz[e] : v[e];
-            x = x * inv * w[(g0 + i + e) % w_len];
-            out[(size_t)t * width + g0 + i + e] = from_f32<T>(gate_first ? x : x * gz[e]);
+    for (int k = 0; k < TRIPS; ++k) {
+        const int i = k * 128 + lane * 4;
+        if (i < group) {
+            float o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float x = v[k][e] * inv * w[(g0 + i + e) % w_len];
+                o[e] = gate_first ? x : x * gz[k][e];
+            }
+            T* dst = out + (size_t)t * width + g0 + i;
+            if (wide_rows) {
+                if (sizeof(T) == 4) {
+                    *reinterpret_cast<float4*>(dst) = make_float4(o[0], o[1], o[2], o[3]);
+                } else {
+                    uint2 u;
+                    *reinterpret_cast<__nv_bfloat162*>(&u.x) = __floats2bfloat162_rn(o[0], o[1]);
+                    *reinterpret_cast<__nv_bfloat162*>(&u.y) = __floats2bfloat162_rn(o[2], o[3]);
+                    *reinterpret_cast<uint2*>(dst) = u;
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) dst[e] = from_f32<T>(o[e]);
+            }
         }
     }
 }
@@ -438,12 +521,14 @@ TI_API int ti_gated_group_norm(void* out, const float* y, const void* gate, int 
     if (group % 4 == 0 && group <= 512 && (uintptr_t)y % 16 == 0) {          // a warp a group; larger groups: a block
         const long long num_groups = (long long)num_tokens * (width / group);
         const unsigned blocks = (unsigned)((num_groups + 7) / 8);
+        const int wide_rows = (uintptr_t)out % 16 == 0;          // width and group are multiples of four: rows of out start on 8 or 16 bytes
         if (dtype == TI_F32)
             ti_launch(gated_group_norm_warp_kernel<float>, blocks, 256, 0, stream, (float*)out, y, (const float*)gate, ld_gate,
-                      gate_off, w, w_len, width, group, eps, gate_first, out_scale, num_groups);
+                      gate_off, w, w_len, width, group, eps, gate_first, out_scale, num_groups, wide_rows);
         else if (dtype == TI_BF16)
             ti_launch(gated_group_norm_warp_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)out, y,
-                      (const __nv_bfloat16*)gate, ld_gate, gate_off, w, w_len, width, group, eps, gate_first, out_scale, num_groups);
+                      (const __nv_bfloat16*)gate, ld_gate, gate_off, w, w_len, width, group, eps, gate_first, out_scale, num_groups,
+                      wide_rows);
         else TI_REQUIRE(false, "gated_group_norm: unknown dtype %d", dtype);
         TI_CHECK_LAUNCH("gated_group_norm");
         return 0;

@@ -100,7 +100,7 @@ _SIGNATURES = {
         "ti_linear_scan": [c_void_p, c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
                            c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_float, c_void_p,
                            c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_ll, c_void_p, c_int, c_void_p],
-        "ti_linear_scan_scratch_floats": [c_int, c_int, c_int, c_int, c_int],
+        "ti_linear_scan_scratch_floats": [c_int, c_int, c_int, c_int, c_int, c_int],
         "ti_gated_group_norm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float,
                                 c_int, c_float, c_int, c_void_p],
     },
@@ -1328,7 +1328,7 @@ def linear_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: ScanGat
     if stretches > 1:
         fn = _fn("hybrid", "ti_linear_scan_scratch_floats")
         fn.restype = ctypes.c_longlong
-        scratch = torch.empty(int(fn(num_seqs, heads, key_dim, value_dim, stretches)), dtype=torch.float32, device=q.device)
+        scratch = torch.empty(int(fn(num_seqs, t, heads, key_dim, value_dim, stretches)), dtype=torch.float32, device=q.device)
     made = None          # the decays (and the keys' factors) as the scan reads them, unless the gate holds them already
     if gate.kind != "raw" and stretches > 1:
         made = torch.empty(t * heads * (key_dim if gate.per_channel else 1) * (2 if gate.kind == "step_size" else 1),
