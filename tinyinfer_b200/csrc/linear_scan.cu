@@ -533,8 +533,8 @@ TI_API int ti_gated_group_norm(void* out, const float* y, const void* gate, int 
         TI_CHECK_LAUNCH("gated_group_norm");
         return 0;
     }
-    int threads = 32;
-    while (threads < 256 && threads < group) threads <<= 1;
+    int threads = 32;          // a thread's trips wait for one another's loads: as many threads as a block may have
+    while (threads < 1024 && threads < group) threads <<= 1;
     dim3 grid(num_tokens, width / group);
     if (dtype == TI_F32)
         ti_launch(gated_group_norm_kernel<float>, grid, threads, 0, stream, (float*)out, y, (const float*)gate, ld_gate, gate_off,
