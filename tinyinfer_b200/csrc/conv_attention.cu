@@ -125,7 +125,7 @@ __global__ void short_conv_vec_kernel(T* __restrict__ out, const T* __restrict__
 
 template <typename T>
 __global__ void conv_qkv_append_vec_kernel(T* __restrict__ q_out, T* __restrict__ cache, const T* __restrict__ qkv,
-                                           const float* __restrict__ state, long long slot_stride,
+                                           int ld_in, int in_off, const float* __restrict__ state, long long slot_stride,
                                            const float* __restrict__ w, int taps, float temp_coef, int temp_every,
                                            const int* __restrict__ positions, const int* __restrict__ token_seq,
                                            const int* __restrict__ cu_seqlens, const int* __restrict__ state_slots,
@@ -143,7 +143,7 @@ __global__ void conv_qkv_append_vec_kernel(T* __restrict__ q_out, T* __restrict_
     const int local = t - cu_seqlens[seq];
     const float* hist = taps > 1 ? state + (size_t)state_slots[seq] * slot_stride : nullptr;
     float acc[V], newest[V];
-    conv_at_vec<T, V>(qkv, width, c0, t, local, hist, width, c0, w, taps, acc, newest);
+    conv_at_vec<T, V>(qkv, ld_in, in_off + c0, t, local, hist, width, c0, w, taps, acc, newest);
     if (shift_history && taps > 1) {
 #pragma unroll
         for (int i = 0; i < V; ++i) conv_shift_history(const_cast<float*>(hist), width, c0 + i, taps, newest[i]);
@@ -272,8 +272,8 @@ TI_API int ti_conv_state_update(float* state, long long slot_stride, const void*
 }
 
 template <typename T>
-__global__ void conv_qkv_append_kernel(T* __restrict__ q_out, T* __restrict__ cache, const T* __restrict__ qkv,
-                                       const float* __restrict__ state, long long slot_stride, const float* __restrict__ w,
+__global__ void conv_qkv_append_kernel(T* __restrict__ q_out, T* __restrict__ cache, const T* __restrict__ qkv, int ld_in,
+                                       int in_off, const float* __restrict__ state, long long slot_stride, const float* __restrict__ w,
                                        int taps, float temp_coef, int temp_every, const int* __restrict__ positions,
                                        const int* __restrict__ token_seq, const int* __restrict__ cu_seqlens,
                                        const int* __restrict__ state_slots, const int* __restrict__ block_table,
@@ -288,9 +288,10 @@ __global__ void conv_qkv_append_kernel(T* __restrict__ q_out, T* __restrict__ ca
     const int seq = token_seq[t];
     const int local = t - cu_seqlens[seq];
     const float* hist = taps > 1 ? state + (size_t)state_slots[seq] * slot_stride : nullptr;
-    float v = taps > 1 ? conv_at(qkv, width, c, t, local, hist, width, c, w, taps)
-                       : (w ? w[c] : 1.f) * to_f32(qkv[(size_t)t * width + c]);     // one tap: [1][width]
-    if (shift_history && taps > 1) conv_shift_history(const_cast<float*>(hist), width, c, taps, to_f32(qkv[(size_t)t * width + c]));
+    float v = taps > 1 ? conv_at(qkv, ld_in, in_off + c, t, local, hist, width, c, w, taps)
+                       : (w ? w[c] : 1.f) * to_f32(qkv[(size_t)t * ld_in + in_off + c]);     // one tap: [1][width]
+    if (shift_history && taps > 1)
+        conv_shift_history(const_cast<float*>(hist), width, c, taps, to_f32(qkv[(size_t)t * ld_in + in_off + c]));
     const int pos = positions[t];
     if (c < cq) {
         if (temp_every > 0) v *= 1.f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.f);
@@ -313,8 +314,8 @@ __global__ void conv_qkv_append_kernel(T* __restrict__ q_out, T* __restrict__ ca
 
 // w: float32 [taps][width] over the packed channels (may be null with taps == 1: no convolution at all).
 // planes 1: cache [pages][hkv][page_size][d + dv]; planes 2 (d == dv): [2][pages][hkv][page_size][d].
-// shift_history: as in ti_short_conv.
-TI_API int ti_conv_qkv_append(void* q_out, void* cache, const void* qkv, float* state, long long slot_stride,
+// shift_history: as in ti_short_conv. The packed rows are columns [in_off, in_off + width) of rows of ld_in elements.
+TI_API int ti_conv_qkv_append(void* q_out, void* cache, const void* qkv, int ld_in, int in_off, float* state, long long slot_stride,
                               const float* w, int taps, float temp_coef, int temp_every, const int* positions,
                               const int* token_seq, const int* cu_seqlens, const int* state_slots, const int* block_table,
                               int max_blocks, int num_tokens, int hq, int hkv, int d, int dv, int page_size, int num_pages,
@@ -330,17 +331,18 @@ TI_API int ti_conv_qkv_append(void* q_out, void* cache, const void* qkv, float* 
     if (num_tokens == 0) return 0;
     const int width = hq * d + hkv * (d + dv);
     const int vec = dtype == TI_F32 ? 4 : 8;
-    if (num_tokens >= 64 && d % vec == 0 && dv % vec == 0 && ((uintptr_t)q_out | (uintptr_t)cache | (uintptr_t)qkv | (uintptr_t)w) % 16 == 0) {
+    TI_REQUIRE(in_off >= 0 && ld_in >= in_off + width, "conv_qkv_append: the packed rows do not fit their tensor's rows");
+    if (num_tokens >= 64 && d % vec == 0 && dv % vec == 0 && ld_in % vec == 0 && in_off % vec == 0 && ((uintptr_t)q_out | (uintptr_t)cache | (uintptr_t)qkv | (uintptr_t)w) % 16 == 0) {
         dim3 vgrid((width / vec + 127) / 128, num_tokens);
         if (dtype == TI_F32)
             ti_launch(conv_qkv_append_vec_kernel<float>, vgrid, 128, 0, stream, (float*)q_out, (float*)cache, (const float*)qkv,
-                      (const float*)state, slot_stride, w, taps, temp_coef, temp_every, positions, token_seq, cu_seqlens,
+                      ld_in, in_off, (const float*)state, slot_stride, w, taps, temp_coef, temp_every, positions, token_seq, cu_seqlens,
                       state_slots, block_table, max_blocks, hq, hkv, d, dv, page_size, num_pages, row_stride, v_off,
                       shift_history, status);
         else if (dtype == TI_BF16)
             ti_launch(conv_qkv_append_vec_kernel<__nv_bfloat16>, vgrid, 128, 0, stream, (__nv_bfloat16*)q_out,
-                      (__nv_bfloat16*)cache, (const __nv_bfloat16*)qkv, (const float*)state, slot_stride, w, taps, temp_coef,
-                      temp_every, positions, token_seq, cu_seqlens, state_slots, block_table, max_blocks, hq, hkv, d, dv,
+                      (__nv_bfloat16*)cache, (const __nv_bfloat16*)qkv, ld_in, in_off, (const float*)state, slot_stride, w, taps,
+                      temp_coef, temp_every, positions, token_seq, cu_seqlens, state_slots, block_table, max_blocks, hq, hkv, d, dv,
                       page_size, num_pages, row_stride, v_off, shift_history, status);
         else TI_REQUIRE(false, "conv_qkv_append: unknown dtype %d", dtype);
         TI_CHECK_LAUNCH("conv_qkv_append");
@@ -348,12 +350,13 @@ TI_API int ti_conv_qkv_append(void* q_out, void* cache, const void* qkv, float* 
     }
     dim3 grid((width + 127) / 128, num_tokens);
     if (dtype == TI_F32)
-        ti_launch(conv_qkv_append_kernel<float>, grid, 128, 0, stream, (float*)q_out, (float*)cache, (const float*)qkv, (const float*)state,
+        ti_launch(conv_qkv_append_kernel<float>, grid, 128, 0, stream, (float*)q_out, (float*)cache, (const float*)qkv, ld_in, in_off,
+                  (const float*)state,
                   slot_stride, w, taps, temp_coef, temp_every, positions, token_seq, cu_seqlens, state_slots, block_table,
                   max_blocks, hq, hkv, d, dv, page_size, num_pages, row_stride, v_off, shift_history, status);
     else if (dtype == TI_BF16)
         ti_launch(conv_qkv_append_kernel<__nv_bfloat16>, grid, 128, 0, stream, (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache,
-                  (const __nv_bfloat16*)qkv, (const float*)state, slot_stride, w, taps, temp_coef, temp_every, positions, token_seq,
+                  (const __nv_bfloat16*)qkv, ld_in, in_off, (const float*)state, slot_stride, w, taps, temp_coef, temp_every, positions, token_seq,
                   cu_seqlens, state_slots, block_table, max_blocks, hq, hkv, d, dv, page_size, num_pages, row_stride, v_off,
                   shift_history, status);
     else TI_REQUIRE(false, "conv_qkv_append: unknown dtype %d", dtype);

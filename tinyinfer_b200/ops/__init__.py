@@ -92,7 +92,7 @@ _SIGNATURES = {
                           c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "ti_conv_state_update": [c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                  c_void_p],
-        "ti_conv_qkv_append": [c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_void_p, c_int, c_float, c_int, c_void_p,
+        "ti_conv_qkv_append": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_ll, c_void_p, c_int, c_float, c_int, c_void_p,
                                c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                c_int, c_int, c_void_p, c_int, c_void_p],
         "ti_attention_rows": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
@@ -1202,8 +1202,8 @@ def conv_qkv_append(qkv: torch.Tensor, *, num_heads: int, num_kv_heads: int, hea
                     temperature: Optional[tuple], positions: torch.Tensor, token_seq: torch.Tensor,
                     cu_seqlens: torch.Tensor, state_slots: torch.Tensor, cache: Optional[torch.Tensor],
                     block_table: torch.Tensor, status: Optional[torch.Tensor] = None,
-                    shift_history: bool = False) -> torch.Tensor:
-    """``qkv`` [T, Hq d + Hkv (d + dv)] packed [q | k | v]: a short causal convolution per channel
+                    shift_history: bool = False, offset: int = 0) -> torch.Tensor:
+    """Columns [offset, offset + Hq d + Hkv (d + dv)) of ``qkv`` [T, row], packed [q | k | v]: a short causal convolution per channel
     (``conv_weight`` float32 [taps, channels], tap by tap, with ``history`` float32 [slots, taps - 1, channels]; None: none),
     then q times its position's temperature 1 + coef * ln(floor((p + 1) / every) + 1) (``temperature`` =
     (coef, every) or None). Returns q [T, Hq, d]; k and v go to the token's row [k | v] of ``cache``
@@ -1212,8 +1212,8 @@ def conv_qkv_append(qkv: torch.Tensor, *, num_heads: int, num_kv_heads: int, hea
     _check(qkv, "qkv", None, 2)
     t = qkv.shape[0]
     width = num_heads * head_dim + num_kv_heads * (head_dim + v_dim)
-    if qkv.shape[1] != width:
-        raise KernelError("conv_qkv_append: the packed rows do not match the head sizes")
+    if offset < 0 or offset + width > qkv.shape[1]:
+        raise KernelError("conv_qkv_append: the packed rows do not fit the rows they lie in")
     taps, stride = 1, 0
     if conv_weight is not None:
         _check(conv_weight, "conv_weight", torch.float32, 2)
@@ -1231,7 +1231,8 @@ def conv_qkv_append(qkv: torch.Tensor, *, num_heads: int, num_kv_heads: int, hea
         num_pages, page_size = cache.shape[1], cache.shape[3]
     coef, every = (float(temperature[0]), int(temperature[1])) if temperature else (0.0, 0)
     q = torch.empty((t, num_heads, head_dim), dtype=qkv.dtype, device=qkv.device)
-    _run("hybrid", "ti_conv_qkv_append", q.data_ptr(), _ptr(cache), qkv.data_ptr(), history.data_ptr() if taps > 1 else None,
+    _run("hybrid", "ti_conv_qkv_append", q.data_ptr(), _ptr(cache), qkv.data_ptr(), qkv.shape[1], offset,
+         history.data_ptr() if taps > 1 else None,
          stride, _ptr(conv_weight), taps, coef, every, positions.data_ptr(), token_seq.data_ptr(), cu_seqlens.data_ptr(),
          state_slots.data_ptr(), block_table.data_ptr(), block_table.shape[1], t, num_heads, num_kv_heads, head_dim, v_dim,
          page_size, num_pages, planes, int(shift_history), _ptr(status), _dtype_code(qkv), _stream())

@@ -140,6 +140,21 @@ class Mixer(Part):
             raise NotImplementedError(f"{type(self).__name__} cannot scale its output; it cannot stand in a sum of mixers")
         return self.forward(x, step, cache) if residual is None else self.forward_residual(x, residual, step, cache)
 
+    def input_rows(self):
+        """(weight [n, hidden], bias float32 [n] or None) of the product that reads the mixer's input, if the mixer can
+        take that product's result from someone else (``forward_projected``); None otherwise. A mixer of several
+        mixers packs its branches' rows into one product. Once they are taken, the mixer's own copy may be dropped
+        (``drop_input_rows``)."""
+        return None
+
+    def drop_input_rows(self) -> None:
+        pass
+
+    def forward_projected(self, projected, offset: int, x, scale: float, residual, step, cache) -> torch.Tensor:
+        """``forward_scaled`` with the input product already made: its result for this mixer lies in columns
+        [offset, offset + n) of ``projected``."""
+        raise NotImplementedError
+
     def forward_prenorm(self, x, norm: "Norm", link, next_norm: Optional["Norm"], step, cache):
         """x + forward(norm(x)) for ``x`` BEFORE its norm. ``link``: None, or what the part that made x
         left for this norm (an ``ops.NormLink``); ``next_norm``: the norm the result will pass through

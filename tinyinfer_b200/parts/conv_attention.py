@@ -68,10 +68,22 @@ class ConvAttention(Mixer):
             # tap by tap, [taps, channels]: neighbouring channels are neighbours in memory, as the kernel reads them
             self.conv_w = torch.cat([tensors["q.conv"], tensors["k.conv"], tensors["v.conv"]], dim=0).t().contiguous()
 
-    def _attend(self, x, step, cache, out_scale=1.0):
+    def input_rows(self):
+        return self.w_qkv, self.b_qkv
+
+    def drop_input_rows(self):
+        self.w_qkv = self.b_qkv = None
+
+    def forward_projected(self, projected, offset, x, scale, residual, step, cache):
+        bias = self.b_o if self.b_o is None or scale == 1.0 else self._scaled_bias(scale)
+        attended = self._attend(x, step, cache, out_scale=scale, qkv=projected, offset=offset)
+        return ops.linear(attended, self.w_o, bias=bias, residual=residual)
+
+    def _attend(self, x, step, cache, out_scale=1.0, qkv=None, offset=0):
         s = self.spec
         width = sum(self._sizes)
-        qkv = ops.linear(x, self.w_qkv, bias=self.b_qkv)
+        if qkv is None:
+            qkv = ops.linear(x, self.w_qkv, bias=self.b_qkv)
         history = cache.state.unflatten(1, (s.conv_taps - 1, width)) if s.conv_taps > 1 else None
         single = step.num_tokens == step.num_seqs          # every request brings one token: the kernel keeps the history itself
         q = ops.conv_qkv_append(
@@ -79,9 +91,9 @@ class ConvAttention(Mixer):
             conv_weight=self.conv_w, history=history, temperature=s.query_temperature, positions=step.positions,
             token_seq=step.token_seq, cu_seqlens=step.cu_seqlens, state_slots=step.state_slots,
             cache=cache.kv if cache.writes else None, block_table=cache.block_table, status=step.status,
-            shift_history=single and cache.writes)
+            shift_history=single and cache.writes, offset=offset)
         if history is not None and cache.writes and not single:
-            ops.conv_state_update(history, qkv, offset=0, width=width, taps=s.conv_taps, cu_seqlens=step.cu_seqlens,
+            ops.conv_state_update(history, qkv, offset=offset, width=width, taps=s.conv_taps, cu_seqlens=step.cu_seqlens,
                                   state_slots=step.state_slots, num_seqs=step.num_seqs)
         if cache.kv.shape[0] == 2:          # the paged attention of the plain decoder, tensor cores where the sizes allow
             return ops.paged_attention(q, cache.kv, positions=step.positions, token_seq=step.token_seq,

@@ -44,18 +44,29 @@ class GatedLinearAttention(Mixer):
         self.w_a1, self.w_a2, self.b_a2 = tensors["a1"].contiguous(), tensors["a2"].contiguous(), tensors["a2.b"]
         self.norm_w, self.w_o = tensors["norm"], tensors["o"].contiguous()
 
-    def _features(self, x, step, cache, out_scale=1.0):
+    def input_rows(self):
+        return self.w_in, None
+
+    def drop_input_rows(self):
+        self.w_in = None
+
+    def forward_projected(self, projected, offset, x, scale, residual, step, cache):
+        return ops.linear(self._features(x, step, cache, out_scale=scale, packed=projected, at=offset), self.w_o,
+                          residual=residual)
+
+    def _features(self, x, step, cache, out_scale=1.0, packed=None, at=0):
         s = self.spec
         nk, nv = s.num_heads * s.key_dim, s.num_heads * s.value_dim
-        packed = ops.linear(x, self.w_in)                                            # [T, q | k | v | g]
+        if packed is None:
+            packed = ops.linear(x, self.w_in)                                        # [T, q | k | v | g]
         logits = ops.linear(ops.linear(x, self.w_a1), self.w_a2, bias=self.b_a2, out_float32=True)
         state = cache.state.unflatten(1, (s.num_heads, s.value_dim, s.key_dim))
         o = ops.linear_scan(packed, packed, packed, ops.ScanGate("sigmoid_power", logits, per_channel=True, tau=s.tau),
                             state=state, heads=s.num_heads, groups=s.num_heads, key_dim=s.key_dim, value_dim=s.value_dim,
-                            q_offset=0, k_offset=nk, v_offset=2 * nk, q_scale=s.key_dim ** -0.5,
+                            q_offset=at, k_offset=at + nk, v_offset=at + 2 * nk, q_scale=s.key_dim ** -0.5,
                             cu_seqlens=step.cu_seqlens, state_slots=step.state_slots, num_seqs=step.num_seqs, max_q_len=step.max_q_len)
         return ops.gated_group_norm(o, packed, self.norm_w, group=s.value_dim, eps=s.norm_eps, gate_first=False,
-                                    out_dtype=self.dtype, gate_offset=2 * nk + nv, out_scale=out_scale)
+                                    out_dtype=self.dtype, gate_offset=at + 2 * nk + nv, out_scale=out_scale)
 
     def forward(self, x, step, cache):
         return ops.linear(self._features(x, step, cache), self.w_o)

@@ -2,7 +2,8 @@
 registry with its own tensors under its own prefix. The branches' per-request states lie one after the other in
 one state slot, and at most one branch may want pages, so that the cache entry of the layer serves them all.
 The sum costs no kernel: a branch folds its factor into a kernel it launches anyway (``Mixer.forward_scaled``)
-and its output projection adds what the branches before it gave.
+and its output projection adds what the branches before it gave. Branches that say which rows their input
+product has (``Mixer.input_rows``) share ONE product of all those rows, and each reads its columns of the result.
 """
 from __future__ import annotations
 
@@ -48,6 +49,25 @@ class ParallelMixer(Mixer):
     def load(self, tensors):
         for b, prefix in zip(self.branches, self.spec.prefixes):
             b.load({local: tensors[prefix + local] for local in b.tensors()})
+        # one product for the input rows of all branches that can take its result (at least two of them)
+        self.w_in = self.b_in = None
+        self.offsets = [None] * len(self.branches)
+        rows = [b.input_rows() for b in self.branches]
+        if sum(r is not None for r in rows) >= 2:
+            weights, biases, at = [], [], 0
+            for i, r in enumerate(rows):
+                if r is None:
+                    continue
+                self.offsets[i] = at
+                weights.append(r[0])
+                biases.append(r[1] if r[1] is not None else torch.zeros(r[0].shape[0], dtype=torch.float32, device=r[0].device))
+                at += r[0].shape[0]
+            self.w_in = torch.cat(weights, dim=0).contiguous()
+            if any(r is not None and r[1] is not None for r in rows):
+                self.b_in = torch.cat(biases).contiguous()
+            for b, r in zip(self.branches, rows):
+                if r is not None:
+                    b.drop_input_rows()
 
     def _views(self, cache):
         from ..engine.batch import CacheView
@@ -64,15 +84,18 @@ class ParallelMixer(Mixer):
         return self.forward_residual(x, None, step, cache)
 
     def forward_residual(self, x, residual, step, cache):
-        out = residual
-        for b, scale, view in zip(self.branches, self.spec.scales, self._views(cache)):
-            out = b.forward_scaled(x, float(scale), out, step, view)
-        return out
+        return self.forward_scaled(x, 1.0, residual, step, cache)
 
     def forward_scaled(self, x, scale, residual, step, cache):
+        from .. import ops
+        projected = ops.linear(x, self.w_in, bias=self.b_in) if getattr(self, "w_in", None) is not None else None
         out = residual
-        for b, own, view in zip(self.branches, self.spec.scales, self._views(cache)):
-            out = b.forward_scaled(x, float(scale) * float(own), out, step, view)
+        for i, (b, own, view) in enumerate(zip(self.branches, self.spec.scales, self._views(cache))):
+            factor = float(scale) * float(own)
+            if projected is not None and self.offsets[i] is not None:
+                out = b.forward_projected(projected, self.offsets[i], x, factor, out, step, view)
+            else:
+                out = b.forward_scaled(x, factor, out, step, view)
         return out
 
 
